@@ -14,8 +14,8 @@ What is here instead:
   ``[entries, pages, 2 (K,V), kv_heads, page_size, head_dim]``; a page id is
   valid for every entry of its group.  A request has one block table per
   group.  A mixer that caches one vector per token (``PagedVectorNeed``: a
-  latent that keys and values are derived from) joins a group of its width
-  and window, whose tensor is ``[entries, pages, page_size, width]``.
+  latent that keys and values are derived from) joins a group of its width,
+  window and kept first tokens, whose tensor is ``[entries, pages, page_size, width]``.
 * **Pages on demand.**  ``append`` allocates the pages that the tokens of the
   coming step need, in all groups or in none; ``commit`` advances the
   request's length after the step has run (the reference's two-phase
@@ -24,7 +24,7 @@ What is here instead:
   moved past.  ``release`` gives back everything a request holds.
 * **State slots.**  Every live request holds one slot; mixers that ask for
   ``StateNeed`` get a tensor ``[slots, *shape]`` per entry, zeroed for the
-  slot when a request takes it.  Qwen3 has no such mixer; the slots exist so
+  slot when a request takes it (``PagedStateNeed``: pages and such a state).  Qwen3 has no such mixer; the slots exist so
   that one can be added.  ``append`` keeps a copy of the request's slot as it
   is before the step, and ``rollback`` puts it back: a step that did not run
   to its end leaves no half-advanced state.
@@ -49,7 +49,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.registry import PagedKVNeed, PagedVectorNeed, StateNeed
+from ..parts.registry import PagedKVNeed, PagedStateNeed, PagedVectorNeed, StateNeed
 from .pools import OutOfPages, PagePool, StateSlotPool
 
 
@@ -145,6 +145,7 @@ class PagedCacheView:
     page_size: int
     writable: bool                     # False: the entry reads another entry's cache
     window: Optional[int]
+    state: Optional[torch.Tensor] = None   # [slots, *shape]: the entry's per-request state, where its mixer keeps one too
 
 
 @dataclass
@@ -170,8 +171,13 @@ class CacheManager:
         self.state_tensors: Dict[int, torch.Tensor] = {}
         by_key: Dict[Tuple, int] = {}
         for e, need in enumerate(needs):
+            if isinstance(need, PagedStateNeed):              # pages, and a state slot beside them
+                if allocate_tensors:
+                    self.state_tensors[e] = torch.zeros((max_requests,) + tuple(need.state.shape),
+                                                        dtype=need.state.dtype, device=device)
+                need = need.paged
             if isinstance(need, (PagedKVNeed, PagedVectorNeed)):
-                key = (("vector", need.width, need.window) if isinstance(need, PagedVectorNeed)
+                key = (("vector", need.width, need.window, need.keep_first) if isinstance(need, PagedVectorNeed)
                        else (need.kv_heads, need.head_dim, need.window))
                 if key not in by_key:
                     by_key[key] = len(self.groups)
@@ -326,8 +332,11 @@ class CacheManager:
     def _give_back(self, rc: RequestCache) -> None:
         for g, grp in enumerate(self.groups):
             first = self._first_needed_page(grp, rc.confirmed_tokens)
-            if first > rc.first_live[g]:
-                grp.pool.free(rc.pages[g].give_back(rc.first_live[g], first), rc.rid)
+            # pages that hold one of the first tokens a group keeps are never given back
+            kept = -(-getattr(grp.need, "keep_first", 0) // self.page_size)
+            lo = max(rc.first_live[g], kept)
+            if first > lo:
+                grp.pool.free(rc.pages[g].give_back(lo, first), rc.rid)
                 rc.first_live[g] = first
 
     def release(self, rid: Hashable) -> None:
@@ -408,12 +417,10 @@ class CacheManager:
     def view(self, entry: int, block_tables: List[torch.Tensor], slot_mappings: List[torch.Tensor]):
         """The cache view of schedule entry ``entry`` for a step whose per-group
         block tables and slot mappings are given."""
-        if entry in self.state_tensors:
-            return StateCacheView(self.state_tensors[entry])
         if entry not in self.entry_group:
-            return None
+            return StateCacheView(self.state_tensors[entry]) if entry in self.state_tensors else None
         g, idx = self.entry_group[entry]
         grp = self.groups[g]
         return PagedCacheView(kv=grp.kv[idx], block_table=block_tables[g], slot_mapping=slot_mappings[g],
                               page_size=self.page_size, writable=self.reads_cache_of[entry] is None,
-                              window=grp.need.window)
+                              window=grp.need.window, state=self.state_tensors.get(entry))

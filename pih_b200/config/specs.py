@@ -273,11 +273,94 @@ class ScoredMoESpec:
 
 
 @dataclass(frozen=True)
+class ScaledRopeSpec:
+    """Rotation of the first ``rotary_dim`` columns of a head by a table of cosines and sines per position, the pairs
+    being neighbours ``(2i, 2i + 1)`` (``interleaved``) or halves ``(i, i + rotary_dim / 2)``.  With ``factor`` the low
+    frequencies are stretched (YaRN): with ``turn(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta)``,
+    ``lo = max(floor(turn(fast)), 0)``, ``hi = min(ceil(turn(slow)), rotary_dim - 1)`` and ``ramp_i = clamp((i - lo) /
+    max(hi - lo, ramp_floor), 0, 1)`` the frequency of pair i is ``f_i / factor * ramp_i + f_i (1 - ramp_i)``, and
+    cosine and sine are multiplied by ``gain_slope ln(factor) + 1``."""
+    head_dim: int
+    rotary_dim: int
+    theta: float
+    max_positions: int
+    interleaved: bool = True
+    factor: Optional[float] = None       # None: the plain frequencies theta^(-2i / rotary_dim)
+    original: float = 0.0
+    fast: float = 32.0
+    slow: float = 1.0
+    gain_slope: float = 0.1
+    ramp_floor: float = 0.001
+    kind: str = "rope_scaled"
+
+
+@dataclass(frozen=True)
+class WindowAttentionSpec:
+    """Softmax attention over a sliding window of ``window`` keys (the row's own included) and the first ``keep_first``
+    keys of the sequence, with a term ``exp(sink)`` in the denominator that has no key and no value (``sink``
+    "learned": one number a head; "zero": a score of 0, which adds 1; "none").  Options, each a mechanism of its own:
+
+    * ``conv_taps`` > 0: q, k and v pass a short causal convolution per channel right behind their projections (no
+      bias, no activation); a sequence's last ``conv_taps - 1`` projected rows are its state;
+    * ``norm_eps`` not None: q and k are RMS-normed over their WHOLE projection (all heads at once), a weight a column;
+    * ``values_from_keys``: there is no value projection, the values are the keys as projected (before norm and rotation);
+    * ``position``: a rotation of q and k;
+    * ``bias_rows`` > 0: a learned bias ``rel[bucket(distance), head]`` is added to the scaled score, with
+      ``bucket(n) = n`` below ``bias_rows // 2`` and beyond it ``min(bias_rows - 1, half + floor(ln(n / half) /
+      ln(bias_far / half) * (bias_rows - half)))``;
+    * ``softcap``: the scaled score becomes ``softcap * tanh(score / softcap)``;
+    * ``head_gate``: head h's output is multiplied by ``sigmoid`` of a one-row projection of the mixer's input."""
+    hidden: int
+    heads: int
+    kv_heads: int
+    key_dim: int
+    value_dim: int
+    scale: float
+    window: int
+    keep_first: int = 0
+    conv_taps: int = 0
+    norm_eps: Optional[float] = None
+    values_from_keys: bool = False
+    position: Optional[object] = None
+    bias_rows: int = 0
+    bias_far: float = 0.0
+    softcap: Optional[float] = None
+    sink: str = "learned"
+    head_gate: bool = False
+    kind: str = "window_attention"
+    names: Mapping[str, str] = _names(q="mix.q", k="mix.k", v="mix.v", o="mix.o", q_norm="mix.q.norm", k_norm="mix.k.norm",
+                                      q_conv="mix.q.conv", k_conv="mix.k.conv", v_conv="mix.v.conv", bias="mix.rel",
+                                      sink="mix.sink", gate="mix.g")
+
+    @property
+    def q_size(self) -> int:
+        return self.heads * self.key_dim
+
+    @property
+    def k_size(self) -> int:
+        return self.kv_heads * self.key_dim
+
+    @property
+    def v_size(self) -> int:
+        return self.kv_heads * self.value_dim
+
+
+@dataclass(frozen=True)
+class HyperSpec:
+    """Hyper-connections: ``streams`` copies of the residual stream.  A sub-layer reads ``sum_s in[s] x_s`` and its
+    output y is written back as ``x_t <- sum_s mix[s, t] x_s + out[t] y`` for all t at once.  ``names``: the tensors'
+    prefixes for the mixer's and the feed-forward's connections."""
+    streams: int
+    names: Mapping[str, str] = _names(mixer="hc1.", ffn="hc2.")
+
+
+@dataclass(frozen=True)
 class BlockSpec:
     """One layer: ``h += mixer(norm_in(h)); h += ffn(norm_post(h))`` for
     ``arrangement == "prenorm"``; ``h += norm_in(mixer(h)); h += norm_post(ffn(h))``
     for ``arrangement == "outnorm"`` (the norms sit on the sub-layers' outputs,
-    the sub-layers read the stream itself); ``ffn`` and ``norm_post`` None: the layer has
+    the sub-layers read the stream itself); ``arrangement == "hyper"``: the pre-norm
+    layer over several streams (``hyper``); ``ffn`` and ``norm_post`` None: the layer has
     no feed-forward.  ``prefix`` is the layer's tensor-name prefix in the
     weight files."""
     prefix: str
@@ -288,6 +371,7 @@ class BlockSpec:
     arrangement: str = "prenorm"
     names: Mapping[str, str] = _names(norm_in="input_layernorm.",
                                       norm_post="post_attention_layernorm.")
+    hyper: Optional[HyperSpec] = None
 
 
 @dataclass(frozen=True)
@@ -315,6 +399,11 @@ class ModelSpec:
     # "float32": the residual stream is kept and summed in 32-bit whatever the compute dtype (norms read it and
     # give the compute dtype); None: the stream has the compute dtype
     stream_dtype: Optional[str] = None
+    # a learned vector per place, added to the embedding (a table [max_positions, hidden]); None: no such table
+    position_name: Optional[str] = None
+    # > 0: the model keeps this many copies of the residual stream (blocks of the "hyper" arrangement); its output is
+    # the final norm of their sum
+    streams: int = 0
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):

@@ -62,6 +62,18 @@ template <> __device__ __forceinline__ float silu_times<__nv_bfloat16>(float g, 
   return __fdividef(g, 1.0f + __expf(-g)) * u;
 }
 
+// gelu(g) * u with gelu(z) = z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), in 32-bit.  The 32-bit stream uses tanhf;
+// the bf16 stream writes 1 + tanh(a) as 2 - 2 / (e^{2a} + 1) with the special-function unit's exponential.
+template <typename T> __device__ __forceinline__ float gelu_tanh_times(float g, float u);
+template <> __device__ __forceinline__ float gelu_tanh_times<float>(float g, float u) {
+  const float a = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
+  return (0.5f * g * (1.0f + tanhf(a))) * u;
+}
+template <> __device__ __forceinline__ float gelu_tanh_times<__nv_bfloat16>(float g, float u) {
+  const float a = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
+  return (g * (1.0f - __fdividef(1.0f, __expf(2.0f * a) + 1.0f))) * u;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int d = 16; d > 0; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);

@@ -445,7 +445,7 @@ qk_norm_rope_kv_wide_kernel(T* __restrict__ qkv, int row_stride, int rows, int h
 // ---------------------------------------------------------------------------
 // Columns of gate_up come in blocks of 2 * il: il gate columns, then their il up columns (il = inter:
 // all gates, then all ups).
-template <typename T>
+template <typename T, int ACT>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
                                 int inter, int il) {
   wait_for_prior_kernels();
@@ -458,7 +458,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     const int gc = (c / il) * 2 * il + c % il;
     const float g = to_float<T>(gate_up[t * 2 * inter + gc]);
     const float u = to_float<T>(gate_up[t * 2 * inter + gc + il]);
-    out[i] = from_float<T>((g / (1.0f + expf(-g))) * u);
+    out[i] = from_float<T>(ACT == 1 ? gelu_tanh_times<T>(g, u) : (g / (1.0f + expf(-g))) * u);
   }
 }
 
@@ -800,7 +800,7 @@ extern "C" int pih_qk_norm_rope_kv_write(int dtype, int weight_dtype, void* qkv,
 // 2048 x 3072 outputs against 7.7.)
 // 16 bytes per thread and row, two rows per thread with their loads issued together; needs
 // inter * sizeof(T) % 16 == 0 and il a multiple of the vector length.  grid (column vectors / 256, row pairs)
-template <typename T>
+template <typename T, int ACT>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long rows,
                                     int inter, int il) {
   wait_for_prior_kernels();
@@ -828,25 +828,27 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
       uint4 packed;
       T* pk = reinterpret_cast<T*>(&packed);
 #pragma unroll
-      for (int j = 0; j < VEC; ++j) pk[j] = from_float<T>(silu_times<T>(to_float<T>(g[j]), to_float<T>(u[j])));
+      for (int j = 0; j < VEC; ++j)
+        pk[j] = from_float<T>(ACT == 1 ? gelu_tanh_times<T>(to_float<T>(g[j]), to_float<T>(u[j]))
+                                       : silu_times<T>(to_float<T>(g[j]), to_float<T>(u[j])));
       reinterpret_cast<uint4*>(out + (t0 + r) * inter)[c] = packed;
     }
   }
 }
 
-template <typename T>
+template <typename T, int ACT>
 static int launch_silu(const void* gate_up, void* out, long long rows, int inter, int il, cudaStream_t s) {
   const int threads = 256;
   if ((inter * sizeof(T)) % 16 == 0 && il % (16 / sizeof(T)) == 0) {
     const int per_row = inter / (16 / static_cast<int>(sizeof(T)));
     const long long pairs = (rows + 1) / 2;
     const dim3 grid((per_row + threads - 1) / threads, static_cast<unsigned>(pairs < 65535 ? pairs : 65535));
-    launch_kernel(silu_mul_vec_kernel<T>, grid, dim3(threads), 0, s, static_cast<const T*>(gate_up), static_cast<T*>(out),
+    launch_kernel(silu_mul_vec_kernel<T, ACT>, grid, dim3(threads), 0, s, static_cast<const T*>(gate_up), static_cast<T*>(out),
                   rows, inter, il);
   } else {
     const long long total = rows * inter;
     const unsigned blocks = static_cast<unsigned>(min((total + threads - 1) / threads, 148LL * 32));
-    launch_kernel(silu_mul_kernel<T>, dim3(blocks), dim3(threads), 0, s, static_cast<const T*>(gate_up), static_cast<T*>(out), rows,
+    launch_kernel(silu_mul_kernel<T, ACT>, dim3(blocks), dim3(threads), 0, s, static_cast<const T*>(gate_up), static_cast<T*>(out), rows,
                                                   inter, il);
   }
   PIH_LAUNCH_CHECK();
@@ -854,15 +856,25 @@ static int launch_silu(const void* gate_up, void* out, long long rows, int inter
 }
 
 // interleave: gate_up columns come in blocks of `interleave` gate columns followed by their up columns
-// (interleave == inter: all gates, then all ups); it must divide inter.
+// (interleave == inter: all gates, then all ups); it must divide inter.  activation 0: SiLU; 1: GELU in its tanh form.
+extern "C" int pih_act_mul(int dtype, int activation, const void* gate_up, void* out, long long rows, int inter,
+                           int interleave, void* stream) {
+  if (rows <= 0) return 0;
+  if (inter <= 0 || interleave <= 0 || inter % interleave || activation < 0 || activation > 1) return PIH_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (dtype == PIH_F32)
+    return activation == 1 ? launch_silu<float, 1>(gate_up, out, rows, inter, interleave, s)
+                           : launch_silu<float, 0>(gate_up, out, rows, inter, interleave, s);
+  if (dtype == PIH_BF16)
+    return activation == 1 ? launch_silu<__nv_bfloat16, 1>(gate_up, out, rows, inter, interleave, s)
+                           : launch_silu<__nv_bfloat16, 0>(gate_up, out, rows, inter, interleave, s);
+  return PIH_ERR_BAD_ARGUMENT;
+}
+
+// activation 0: SiLU
 extern "C" int pih_silu_mul(int dtype, const void* gate_up, void* out, long long rows, int inter,
                             int interleave, void* stream) {
-  if (rows <= 0) return 0;
-  if (inter <= 0 || interleave <= 0 || inter % interleave) return PIH_ERR_BAD_ARGUMENT;
-  cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == PIH_F32) return launch_silu<float>(gate_up, out, rows, inter, interleave, s);
-  if (dtype == PIH_BF16) return launch_silu<__nv_bfloat16>(gate_up, out, rows, inter, interleave, s);
-  return PIH_ERR_BAD_ARGUMENT;
+  return pih_act_mul(dtype, 0, gate_up, out, rows, inter, interleave, stream);
 }
 
 extern "C" int pih_gather_rows(int dtype, const void* in, const int* rows, void* out, int out_rows,

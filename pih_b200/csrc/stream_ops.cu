@@ -4,6 +4,9 @@
 //   stream_norm_add   h += rmsnorm(y + bias) * w in 32-bit, and beside it the new h rounded to the compute dtype
 //   bias_xielu        act(z + b): for u > 0  ap u^2 + u / 2,  else  an (exp(u) - 1 - u) + u / 2   (32-bit inside)
 //   add_gated         out = a + sigmoid(g[row]) * b   (a shared expert behind its one-number gate)
+//   embed_positions   several copies of embed[token] + positions[place] as 32-bit streams
+//   hyper_stream      several residual streams a row: the pending sub-layer output is written into them through a mixing
+//                     matrix, and the next sub-layer's input is read out of them and normed, in one pass over the row
 #include "common.cuh"
 
 namespace pih {
@@ -91,6 +94,106 @@ __global__ void add_gated_kernel(const T* __restrict__ a, const T* __restrict__ 
   out[i] = from_float<T>(fmaf(g, to_float<T>(b[i]), to_float<T>(a[i])));
 }
 
+// out [rows][streams][width] = embed[token] + positions[place], the same in every stream (32-bit sums).
+template <typename T, typename TO>
+__global__ void embed_positions_kernel(const T* __restrict__ embed, const T* __restrict__ places, const int* __restrict__ ids,
+                                       const int* __restrict__ positions, TO* __restrict__ out, int width, int streams,
+                                       int vocab, int max_positions, uint32_t* __restrict__ error) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long row = blockIdx.x;
+  int id = ids[row], pos = positions[row];
+  if (id < 0 || id >= vocab) {
+    if (threadIdx.x == 0) publish_error(error, kTokenOutOfVocabulary);
+    id = 0;
+  }
+  if (places != nullptr && (pos < 0 || pos >= max_positions)) {
+    if (threadIdx.x == 0) publish_error(error, kBadPosition);
+    pos = 0;
+  }
+  const T* e = embed + static_cast<long long>(id) * width;
+  const T* p = places != nullptr ? places + static_cast<long long>(pos) * width : nullptr;
+  TO* o = out + row * streams * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const TO v = from_float<TO>(to_float<T>(e[c]) + (p != nullptr ? to_float<T>(p[c]) : 0.0f));
+    for (int s = 0; s < streams; ++s) o[static_cast<long long>(s) * width + c] = v;
+  }
+}
+
+constexpr int kMaxStreams = 8;
+
+// One block a row of x [rows][S][width] (32-bit).  With y (the output of the sub-layer that ran last, not yet written):
+//   x_t <- sum_s mix[s][t] x_s + spread[t] y        for all t at once, from the old streams
+// (stored back unless ``gather`` selects rows: then the row is only read).  With ``collect``:
+//   u = sum_t collect[t] x_t;   out = u / sqrt(mean(u^2) + eps) * weight                (weight null: out = u)
+// rounded to TO.  All sums 32-bit, in the order of the streams.
+template <typename TY, typename TO>
+__global__ void __launch_bounds__(256)
+hyper_stream_kernel(float* __restrict__ x, const TY* __restrict__ y, long long ldy, const float* __restrict__ mix,
+                    const float* __restrict__ spread, const float* __restrict__ collect, const float* __restrict__ weight,
+                    const int* __restrict__ gather, TO* __restrict__ out, int S, int width, float eps) {
+  extern __shared__ float hyper_u[];                           // [width]
+  __shared__ float scratch[33];
+  __shared__ float coef[kMaxStreams * kMaxStreams + 2 * kMaxStreams];
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long row = gather != nullptr ? gather[blockIdx.x] : blockIdx.x;
+  float* m = coef;
+  float* sp = coef + kMaxStreams * kMaxStreams;
+  float* co = sp + kMaxStreams;
+  if (threadIdx.x < S * S && y != nullptr) m[threadIdx.x] = mix[threadIdx.x];
+  if (threadIdx.x < S) {
+    sp[threadIdx.x] = y != nullptr ? spread[threadIdx.x] : 0.0f;
+    co[threadIdx.x] = collect != nullptr ? collect[threadIdx.x] : 0.0f;
+  }
+  __syncthreads();
+  float* xr = x + row * S * width;
+  const TY* yr = y != nullptr ? y + row * ldy : nullptr;
+  float ss = 0.0f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    float v[kMaxStreams];
+#pragma unroll
+    for (int s = 0; s < kMaxStreams; ++s) v[s] = s < S ? xr[static_cast<long long>(s) * width + c] : 0.0f;
+    if (yr != nullptr) {
+      const float yv = to_float<TY>(yr[c]);
+      float n[kMaxStreams];
+#pragma unroll
+      for (int t = 0; t < kMaxStreams; ++t) {
+        float acc = 0.0f;
+        if (t < S) {
+#pragma unroll
+          for (int s = 0; s < kMaxStreams; ++s)
+            if (s < S) acc = fmaf(m[s * S + t], v[s], acc);
+          acc = fmaf(sp[t], yv, acc);
+        }
+        n[t] = acc;
+      }
+#pragma unroll
+      for (int t = 0; t < kMaxStreams; ++t) {
+        v[t] = n[t];
+        if (t < S && gather == nullptr) xr[static_cast<long long>(t) * width + c] = n[t];
+      }
+    }
+    if (collect != nullptr) {
+      float u = 0.0f;
+#pragma unroll
+      for (int t = 0; t < kMaxStreams; ++t)
+        if (t < S) u = fmaf(co[t], v[t], u);
+      hyper_u[c] = u;
+      ss = fmaf(u, u, ss);
+    }
+  }
+  if (collect == nullptr) return;
+  float inv = 1.0f;
+  if (weight != nullptr) {
+    ss = block_sum(ss, scratch);
+    inv = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
+  }
+  TO* o = out + static_cast<long long>(blockIdx.x) * width;
+  for (int c = threadIdx.x; c < width; c += blockDim.x)          // (a thread reads back what it wrote itself)
+    o[c] = from_float<TO>(weight != nullptr ? hyper_u[c] * inv * weight[c] : hyper_u[c]);
+}
+
 }  // namespace pih
 
 using namespace pih;
@@ -174,6 +277,62 @@ extern "C" int pih_add_gated(int dtype, const void* a, const void* b, const void
                   static_cast<const float*>(gate), ldg, static_cast<float*>(out), rows, width);
   else
     return PIH_ERR_BAD_ARGUMENT;
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// out [rows, streams, width] of out_dtype = embed[ids] + places[positions] (places null: the embedding alone).
+extern "C" int pih_embed_positions(int dtype, int out_dtype, const void* embed, const void* places, const void* ids,
+                                   const void* positions, void* out, int rows, int width, int streams, int vocab,
+                                   int max_positions, void* error, void* stream) {
+  if (rows <= 0) return 0;
+  if (streams < 1 || width < 1) return PIH_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+#define PIH_EP(T, TO)                                                                                                  \
+  launch_kernel(embed_positions_kernel<T, TO>, dim3(rows), dim3(width >= 1024 ? 256 : 128), 0, s,                      \
+                static_cast<const T*>(embed), static_cast<const T*>(places), static_cast<const int*>(ids),             \
+                static_cast<const int*>(positions), static_cast<TO*>(out), width, streams, vocab, max_positions,       \
+                static_cast<uint32_t*>(error))
+  if (dtype == PIH_BF16 && out_dtype == PIH_F32) PIH_EP(bf16, float);
+  else if (dtype == PIH_F32 && out_dtype == PIH_F32) PIH_EP(float, float);
+  else if (dtype == PIH_BF16 && out_dtype == PIH_BF16) PIH_EP(bf16, bf16);
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_EP
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// x fp32 [*, streams, width] in place; y [rows, ldy] of y_dtype or null (then mix and spread are not read); mix fp32
+// [streams, streams] indexed [from, to]; spread, collect fp32 [streams]; weight fp32 [width] or null; gather int32
+// [out_rows] or null (null: out_rows rows from the first); out [out_rows, width] of out_dtype (null without collect).
+extern "C" int pih_hyper_stream(int y_dtype, int out_dtype, void* x, const void* y, long long ldy, const void* mix,
+                                const void* spread, const void* collect, const void* weight, const void* gather, void* out,
+                                int out_rows, int streams, int width, float eps, void* stream) {
+  if (out_rows <= 0) return 0;
+  if (streams < 1 || streams > kMaxStreams || (collect != nullptr && out == nullptr) || (y == nullptr && collect == nullptr))
+    return PIH_ERR_BAD_ARGUMENT;
+  if (static_cast<size_t>(width) * sizeof(float) > 96 * 1024) return PIH_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const size_t smem = collect != nullptr ? static_cast<size_t>(width) * sizeof(float) : 0;
+  const dim3 grid(out_rows), block(width >= 1024 ? 256 : 128);
+#define PIH_HS(TY, TO)                                                                                                 \
+  do {                                                                                                                 \
+    static bool raised = false;                                                                                        \
+    if (!raised && smem > 48 * 1024) {                                                                                 \
+      cudaFuncSetAttribute(hyper_stream_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);       \
+      raised = true;                                                                                                   \
+    }                                                                                                                  \
+    launch_kernel(hyper_stream_kernel<TY, TO>, grid, block, smem, s, static_cast<float*>(x), static_cast<const TY*>(y), \
+                  ldy, static_cast<const float*>(mix), static_cast<const float*>(spread),                              \
+                  static_cast<const float*>(collect), static_cast<const float*>(weight), static_cast<const int*>(gather), \
+                  static_cast<TO*>(out), streams, width, eps);                                                         \
+  } while (0)
+  if (y_dtype == PIH_BF16 && out_dtype == PIH_BF16) PIH_HS(bf16, bf16);
+  else if (y_dtype == PIH_F32 && out_dtype == PIH_F32) PIH_HS(float, float);
+  else if (y_dtype == PIH_BF16 && out_dtype == PIH_F32) PIH_HS(bf16, float);
+  else if (y_dtype == PIH_F32 && out_dtype == PIH_BF16) PIH_HS(float, bf16);
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_HS
   PIH_LAUNCH_CHECK();
   return 0;
 }

@@ -80,7 +80,7 @@ class NativeBlocks:
         from ..parts.swiglu import SwiGLU
         m = block.mixer
         return (type(block.norm_in) is RMSNorm and type(block.norm_post) is RMSNorm and type(m) is PagedAttention
-                and type(block.ffn) is SwiGLU and (m.position is None or type(m.position) is RotaryEncoding)
+                and type(block.ffn) is SwiGLU and block.ffn.spec.activation == "silu" and (m.position is None or type(m.position) is RotaryEncoding)
                 and block.norm_in.weight.dtype == block.norm_post.weight.dtype
                 and (m.q_norm is None) == (m.k_norm is None)
                 and (m.q_norm is None or m.q_norm.dtype == m.k_norm.dtype))

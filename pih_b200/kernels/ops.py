@@ -109,7 +109,9 @@ class CudaOps:
                      "pih_gated_delta_rule", "pih_gated_rmsnorm", "pih_rglru_scan", "pih_latent_write",
                      "pih_latent_attention_generic", "pih_moe_route", "pih_moe_experts", "pih_moe_combine_bf16", "pih_latent_attention_split", "pih_latent_attention_splits", "pih_latent_attention_mma", "pih_batched_gemv",
                      "pih_stream_cast", "pih_stream_norm_add", "pih_bias_xielu", "pih_add_gated", "pih_retention",
-                     "pih_diff_qk_prepare", "pih_diff_attention", "pih_diff_attention_tile_takes", "pih_moe_route_scored"):
+                     "pih_diff_qk_prepare", "pih_diff_attention", "pih_diff_attention_tile_takes", "pih_moe_route_scored",
+                     "pih_act_mul", "pih_embed_positions", "pih_hyper_stream", "pih_window_qk_prepare",
+                     "pih_window_attention", "pih_window_attention_tile_takes"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
@@ -543,6 +545,17 @@ class CudaOps:
         self._check(rc, "gather_rows")
         return out
 
+    def act_mul(self, gate_up: torch.Tensor, interleave: Optional[int] = None, activation: str = "silu") -> torch.Tensor:
+        """``act(g) * u`` with ``activation`` "silu" or "gelu_tanh" (``g / 2 (1 + tanh(sqrt(2 / pi) (g + 0.044715
+        g^3)))``), in 32-bit, rounded once; columns as for ``silu_mul``."""
+        rows, two_i = gate_up.shape
+        inter = two_i // 2
+        out = torch.empty(rows, inter, dtype=gate_up.dtype, device=gate_up.device)
+        rc = self.lib.pih_act_mul(_DT[gate_up.dtype], {"silu": 0, "gelu_tanh": 1}[activation], _ptr(gate_up), _ptr(out),
+                                  c_ll(rows), inter, interleave if interleave is not None else inter, self._stream())
+        self._check(rc, "act_mul")
+        return out
+
     def silu_mul(self, gate_up: torch.Tensor, interleave: Optional[int] = None) -> torch.Tensor:
         """``silu(g) * u``; the columns of ``gate_up`` come in blocks of ``interleave`` gate columns
         followed by their up columns (default: all gates, then all ups)."""
@@ -964,3 +977,107 @@ class CudaOps:
         return out
 
     diff_attention_fast = True             # False: bf16 steps use the in-order warp kernel too
+
+    # -- several residual streams -------------------------------------------------------------------------------------
+    def embed_positions(self, table: torch.Tensor, places: Optional[torch.Tensor], ids: torch.Tensor,
+                        positions: torch.Tensor, streams: int = 1, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+        """``[rows, streams, width]``: ``table[ids] + places[positions]`` (summed in 32-bit; ``places`` None: the
+        table's rows alone), the same in every stream."""
+        rows, (vocab, width) = ids.shape[0], table.shape
+        assert table.is_contiguous() and (places is None or (places.is_contiguous() and places.dtype == table.dtype
+                                                             and places.shape[1] == width))
+        out = torch.empty(rows, streams, width, dtype=out_dtype, device=table.device)
+        rc = self.lib.pih_embed_positions(_DT[table.dtype], _DT[out_dtype], _ptr(table), _ptr(places), _ptr(ids),
+                                          _ptr(positions), _ptr(out), rows, width, streams, vocab,
+                                          places.shape[0] if places is not None else 0, self._err(), self._stream())
+        self._check(rc, "embed_positions")
+        return out
+
+    def hyper_stream(self, x: torch.Tensor, y: Optional[torch.Tensor], *, mix=None, spread=None, collect=None, weight=None,
+                     eps: float = 0.0, rows: Optional[torch.Tensor] = None, out_dtype: Optional[torch.dtype] = None):
+        """One pass over the rows of the streams ``x`` (fp32 ``[T, S, width]``, in place).  With ``y [T, width]`` (a
+        sub-layer's output that is not written yet): ``x_t <- sum_s mix[s, t] x_s + spread[t] y`` for all t at once.
+        With ``collect`` (fp32 ``[S]``): returns ``u = sum_t collect[t] x_t`` of the new streams as ``[T, width]`` of
+        ``out_dtype``, RMS-normed with ``weight`` (fp32 ``[width]``) and ``eps`` where a weight is given.  ``rows``
+        (int32): only these rows are read, and nothing is stored.  Sums and norm are 32-bit."""
+        T, S, width = x.shape
+        assert x.dtype == torch.float32 and x.is_contiguous() and (y is None or (y.stride(1) == 1 and y.shape == (T, width)))
+        n_out = T if rows is None else rows.shape[0]
+        out = None
+        if collect is not None:
+            out = torch.empty(n_out, width, dtype=out_dtype or torch.float32, device=x.device)
+        rc = self.lib.pih_hyper_stream(_DT[y.dtype] if y is not None else 0, _DT[out.dtype] if out is not None else 0,
+                                       _ptr(x), _ptr(y), c_ll(y.stride(0) if y is not None else 0), _ptr(mix), _ptr(spread),
+                                       _ptr(collect), _ptr(weight), _ptr(rows), _ptr(out), n_out, S, width, c_float(eps),
+                                       self._stream())
+        self._check(rc, "hyper_stream")
+        return out
+
+    # -- attention over a window with a sink --------------------------------------------------------------------------
+    def window_qk_prepare(self, src: torch.Tensor, *, q_norm, k_norm, eps: float, rope_table, rotary_dim: int,
+                          interleaved: bool, positions, slot_mapping, cache: torch.Tensor, heads: int, kv_heads: int,
+                          key_dim: int, value_dim: int, values_from_keys: bool) -> torch.Tensor:
+        """Rows ``[q: heads x key_dim | k: kv_heads x key_dim | v: kv_heads x value_dim]`` (no v columns with
+        ``values_from_keys``: the values are the key columns as they come).  q and k are RMS-normed over their whole
+        width (fp32 weights a column, or None) and rotated by ``rope_table`` (fp32 ``[positions, rotary_dim / 2,
+        2]``, pairs of neighbours with ``interleaved``, else halves); q is returned as ``[T, heads x key_dim]``, k and v
+        go to the rows' slots of ``cache [pages, page_size, kv_heads (key_dim + value_dim)]``."""
+        rows = src.shape[0]
+        num_pages, page_size, width = cache.shape
+        assert src.stride(1) == 1 and cache.dtype == src.dtype and width == kv_heads * (key_dim + value_dim)
+        assert src.shape[1] >= heads * key_dim + kv_heads * key_dim + (0 if values_from_keys else kv_heads * value_dim)
+        q = torch.empty(rows, heads * key_dim, dtype=src.dtype, device=src.device)
+        rot = rotary_dim if rope_table is not None else 0
+        rc = self.lib.pih_window_qk_prepare(_DT[src.dtype], _ptr(src), c_ll(src.stride(0)), _ptr(q), _ptr(q_norm),
+                                            _ptr(k_norm), c_float(eps), _ptr(rope_table), rot, 1 if interleaved else 0,
+                                            rope_table.shape[0] if rope_table is not None else 0, _ptr(positions),
+                                            _ptr(slot_mapping), _ptr(cache), page_size, num_pages, rows, heads, kv_heads,
+                                            key_dim, value_dim, 1 if values_from_keys else 0, self._err(), self._stream())
+        self._check(rc, "window_qk_prepare")
+        return q
+
+    def window_attention(self, q: torch.Tensor, *, cache: torch.Tensor, block_table: torch.Tensor, step, scale: float,
+                         window: int, keep_first: int, softcap: float, bias: Optional[torch.Tensor],
+                         sink: Optional[torch.Tensor], gate: Optional[torch.Tensor], heads: int, kv_heads: int,
+                         key_dim: int, value_dim: int) -> torch.Tensor:
+        """Attention of the step's rows (q prepared, ``[T, heads x key_dim]``) over the keys of their window and the
+        kept first keys; ``bias`` fp32 ``[heads, distances]`` by distance (the last column for every larger one),
+        ``softcap`` 0: none, ``sink`` fp32 ``[heads]`` or None, ``gate`` ``[T, >= heads]`` (a view: column h is head
+        h's logit) or None.  Returns ``[T, heads x value_dim]``.
+
+        32-bit: a warp a (row, head) over the row's keys in a fixed order (the result does not depend on the step's
+        make-up).  bf16: requests of more than 16 rows on the tensor-core kernel when it has an instance for the
+        sizes, the other rows on the warp kernel with their keys cut into parts that run side by side."""
+        rows = q.shape[0]
+        num_pages, page_size = cache.shape[0], cache.shape[1]
+        assert q.is_contiguous() and cache.dtype == q.dtype and (gate is None or (gate.dtype == q.dtype and gate.stride(1) == 1))
+        out = torch.empty(rows, heads * value_dim, dtype=q.dtype, device=q.device)
+        tile, small, splits, partial = 0, 1, 1, None
+        if q.dtype == torch.bfloat16 and self.window_attention_fast:
+            plans = getattr(step, "attention_plans", None)
+            plan = plans[1] if plans is not None and 1 in plans else None
+            if plan is None:
+                plan = self.attention_plan(step.host_cu_q, step.host_q_start, 1)
+                if plans is not None:
+                    plans[1] = plan
+            if self.lib.pih_window_attention_tile_takes(key_dim, value_dim) and cache.shape[2] % 8 == 0:
+                tile, small = (1 if plan[0] > 0 else 0), (1 if plan[1] > 0 else 0)
+            if small:
+                # a row reads at most its window and the kept keys: as many parts as bring the GPU's warps to work,
+                # and no more than leave a part 128 keys
+                reach = plan[2] if window <= 0 else min(plan[2], window + keep_first + 32)
+                splits = max(1, min(32, (148 * 16) // max(1, rows * heads), max(1, reach // 128)))
+                if splits > 1:
+                    partial = torch.empty(rows * heads * splits * (2 + value_dim), dtype=torch.float32, device=q.device)
+        distances = bias.shape[1] if bias is not None else 0
+        rc = self.lib.pih_window_attention(
+            _DT[q.dtype], _ptr(q), _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1],
+            _ptr(step.request_of_row), _ptr(step.positions), _ptr(step.cu_q), _ptr(getattr(step, "q_start", None)), rows,
+            step.num_requests, heads, kv_heads, key_dim, value_dim, page_size, num_pages, c_float(scale),
+            c_float(softcap or 0.0), _ptr(bias), distances, int(window), int(keep_first), _ptr(sink), _ptr(gate),
+            c_ll(gate.stride(0) if gate is not None else 0), tile, small, splits, _ptr(partial), self._err(), self._stream())
+        self._check(rc, "window_attention")
+        self.launches += tile + (1 if splits > 1 else 0) + small - 1
+        return out
+
+    window_attention_fast = True           # False: bf16 steps use the in-order warp kernel too

@@ -22,12 +22,14 @@ from ..config.specs import ModelSpec
 from ..parts import part_class
 from ..parts.registry import Runtime, TensorInfo
 from ..parts._bind import bind_matrix
-from ..weights.loader import load_weights
+from ..weights.loader import load_weights, tensor_shapes
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, TensorInfo]:
     """Every tensor the model reads, by its name in the weight files."""
     out = {spec.embed_name: TensorInfo((spec.vocab, spec.hidden))}
+    if spec.position_name is not None:
+        out[spec.position_name] = TensorInfo((spec.max_positions, spec.hidden))
     for block in spec.blocks:
         cls = part_class("block", block.arrangement)
         for rel, info in cls.expected_tensors(block).items():
@@ -47,6 +49,8 @@ class CausalLM:
         self.rt = rt
         self.embed = bind_matrix(weights[spec.embed_name], rt)
         self.head = self.embed if spec.tie_embeddings else bind_matrix(weights[spec.head_name], rt)
+        self.places = bind_matrix(weights[spec.position_name], rt) if spec.position_name is not None else None
+        self._ones = torch.ones(spec.streams, dtype=torch.float32, device=rt.device) if spec.streams else None
         self.blocks = []
         for block in spec.blocks:
             cls = part_class("block", block.arrangement)
@@ -80,7 +84,15 @@ class CausalLM:
         schedule entry i.  Returns fp32 logits ``[len(step.logit_rows), vocab]``
         or None when no logits are wanted."""
         ops = self.rt.ops
-        if self.spec.stream_dtype == "float32" and self.rt.dtype != torch.float32:
+        wide = self.spec.stream_dtype == "float32" and self.rt.dtype != torch.float32
+        if self.spec.streams:
+            # several residual streams, 32-bit, all equal to the embedding at the start; ``delta`` is the last
+            # sub-layer's output with the coefficients that write it into the streams
+            h = ops.embed_positions(self.embed, self.places, step.token_ids, step.positions, streams=self.spec.streams)
+        elif self.places is not None:
+            h = ops.embed_positions(self.embed, self.places, step.token_ids, step.positions,
+                                    out_dtype=torch.float32 if wide else self.rt.dtype).reshape(-1, self.spec.hidden)
+        elif wide:
             h = ops.embedding(self.embed, step.token_ids, out_dtype=torch.float32)      # the residual stream stays 32-bit
         else:
             h = ops.embedding(self.embed, step.token_ids)
@@ -89,13 +101,21 @@ class CausalLM:
             h, delta = self.blocks[entry.layer].forward(h, delta, step, caches[i])
         if step.num_logit_rows == 0:
             return None
-        xn = self.final_norm.add_forward(h, delta, rows=step.logit_rows)
+        if self.spec.streams:
+            # the model's output is the final norm of the streams' sum, for the wanted rows
+            y, mix, spread = delta if delta is not None else (None, None, None)
+            xn = ops.hyper_stream(h, y, mix=mix, spread=spread, collect=self._ones, weight=self.final_norm.weight_f32,
+                                  eps=self.final_norm.spec.eps, rows=step.logit_rows, out_dtype=self.rt.dtype)
+        else:
+            xn = self.final_norm.add_forward(h, delta, rows=step.logit_rows)
         return ops.linear(xn, self.head, out_dtype=torch.float32)
 
 
 def load_model(model_dir: str, rt: Runtime):
     """config.json -> registered configuration -> spec -> weights -> CausalLM."""
     config = load_config(model_dir)
+    if hasattr(config, "with_shapes"):                 # sizes that only the tensors' shapes give
+        config = config.with_shapes(tensor_shapes(model_dir))
     spec = config.model_spec()
     expected = {n: i.shape for n, i in expected_tensors(spec).items()}
     optional = {spec.head_name: (spec.vocab, spec.hidden)} if spec.tie_embeddings else {}

@@ -1,8 +1,8 @@
 """Model parts: mixers, feed-forwards, norms, position encodings, blocks."""
-from .registry import (PagedKVNeed, PagedVectorNeed, Runtime, StateNeed, TensorInfo, part_class, register_block,
+from .registry import (PagedKVNeed, PagedStateNeed, PagedVectorNeed, Runtime, StateNeed, TensorInfo, part_class, register_block,
                        register_ffn, register_mixer, register_norm, register_position, unregister)
 from . import (norm, rope, attention, swiglu, block, gated_delta, rglru, latent_attention, moe, retention,  # noqa: F401
-               diff_attention, biased_mlp, scored_moe)                 # (registers the built-in kinds)
+               diff_attention, biased_mlp, scored_moe, window_attention)                 # (registers the built-in kinds)
 
-__all__ = ["PagedKVNeed", "PagedVectorNeed", "Runtime", "StateNeed", "TensorInfo", "part_class", "register_block",
+__all__ = ["PagedKVNeed", "PagedStateNeed", "PagedVectorNeed", "Runtime", "StateNeed", "TensorInfo", "part_class", "register_block",
            "register_ffn", "register_mixer", "register_norm", "register_position", "unregister"]

@@ -11,7 +11,9 @@ A layer whose spec has no feed-forward is ``h += mixer(norm_in(h))`` alone.
 """
 from __future__ import annotations
 
-from .registry import Runtime, part_class, register_block
+import torch
+
+from .registry import Runtime, TensorInfo, part_class, register_block
 
 
 def _sub(weights, names, prefix=""):
@@ -116,3 +118,57 @@ class OutNormBlock:
             y = self.ffn.forward(self._input(h, step))
             self._add(h, y, self.norm_post, step, bias=getattr(self.ffn, "output_bias", None))
         return h, None
+
+
+@register_block("hyper")
+class HyperBlock:
+    """A pre-norm layer over several residual streams (``spec.hyper``: hyper-connections).  The streams ``x`` are
+    32-bit ``[T, S, width]``.  For each sub-layer (the mixer, then the feed-forward) with its learned ``in [S]``,
+    ``out [S]`` and ``mix [S, S]`` (indexed [from, to])::
+
+        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y      (all t at once)
+
+    One kernel pass over a row writes the pending ``y`` of the sub-layer before into the streams and reads the next
+    ``u`` out of them, normed and rounded to the compute dtype; so the block hands on ``(x, pending)`` where
+    ``pending = (y, mix, out)`` of its last sub-layer, for the next block's first pass (or the model's last)."""
+
+    @classmethod
+    def expected_tensors(cls, spec):
+        out = PreNormBlock.expected_tensors.__func__(cls, spec)
+        S = spec.hyper.streams
+        subs = ["mixer"] + (["ffn"] if spec.ffn is not None else [])
+        for sub in subs:
+            p = spec.hyper.names[sub]
+            out[p + "in"] = TensorInfo((S,), "unit_normal")
+            out[p + "out"] = TensorInfo((S,), "unit_normal")
+            out[p + "mix"] = TensorInfo((S, S), "unit_normal")
+        return out
+
+    def __init__(self, spec, weights, rt: Runtime):
+        PreNormBlock.__init__(self, spec, weights, rt)
+        for norm in (self.norm_in, self.norm_post):
+            if norm is not None and not hasattr(norm, "weight_f32"):
+                raise TypeError("a layer over several streams norms with a weight vector")
+        f32 = dict(device=rt.device, dtype=torch.float32)
+        self.links = {}
+        for sub in ("mixer", "ffn"):
+            if sub == "ffn" and spec.ffn is None:
+                continue
+            p = spec.hyper.names[sub]
+            self.links[sub] = tuple(weights[p + r].to(**f32).contiguous() for r in ("in", "mix", "out"))
+
+    def _read(self, x, pending, sub, norm):
+        """Write the pending output into the streams, then the input of sub-layer ``sub``."""
+        collect, _, _ = self.links[sub]
+        y, mix, spread = pending if pending is not None else (None, None, None)
+        return self.rt.ops.hyper_stream(x, y, mix=mix, spread=spread, collect=collect, weight=norm.weight_f32,
+                                        eps=norm.spec.eps, out_dtype=self.rt.dtype)
+
+    def forward(self, x, pending, step, cache):
+        u = self._read(x, pending, "mixer", self.norm_in)
+        y = self.mixer.forward(u, step, cache)
+        pending = (y, self.links["mixer"][1], self.links["mixer"][2])
+        if self.ffn is not None:
+            u = self._read(x, pending, "ffn", self.norm_post)
+            pending = (self.ffn.forward(u), self.links["ffn"][1], self.links["ffn"][2])
+        return x, pending

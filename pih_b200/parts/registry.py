@@ -19,7 +19,7 @@ norm          ``forward(x) -> y`` and ``add_forward(h, delta) -> y`` which
 position      ``rotation_table() -> fp32 [max_positions, rotary_dim/2, 2]``
               (cos, sin) or None, and ``rotary_dim``; used by a mixer that
               rotates q and k.  Must be a pure function of the position.
-mixer         ``cache_need() -> PagedKVNeed | PagedVectorNeed | StateNeed | None`` and
+mixer         ``cache_need() -> PagedKVNeed | PagedVectorNeed | StateNeed | PagedStateNeed | None`` and
               ``forward(x, step, cache) -> y`` with x, y ``[T, hidden]``;
               ``step`` is the engine's ``StepBatch`` (packed rows, request
               boundaries ``cu_q``, positions, state slots), ``cache`` the
@@ -53,9 +53,11 @@ class PagedKVNeed:
 @dataclass(frozen=True)
 class PagedVectorNeed:
     """One vector of ``width`` numbers per token (a latent that keys and values are derived from), in pages
-    like keys and values: the group's tensor is ``[entries, pages, page_size, width]``."""
+    like keys and values: the group's tensor is ``[entries, pages, page_size, width]``.  With a ``window``, the
+    pages that hold one of the first ``keep_first`` tokens stay when the window has moved past them."""
     width: int
     window: Optional[int] = None
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -63,6 +65,14 @@ class StateNeed:
     """Per-request state of fixed size, kept in a state slot."""
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class PagedStateNeed:
+    """A paged cache and, beside it, a per-request state in a state slot (a mixer that caches keys and values per
+    token and also carries a few rows from step to step): the mixer's view is the paged one with ``state`` set."""
+    paged: object                 # PagedKVNeed or PagedVectorNeed
+    state: StateNeed
 
 
 @dataclass

@@ -70,3 +70,64 @@ class ComputedRotary:
     def frequencies(self):
         """fp32 [rotary_dim / 2]."""
         return self._frequencies
+
+
+@register_position("rope_scaled")
+class ScaledRotary:
+    """A table of (cos, sin) per position whose low frequencies may be stretched (``ScaledRopeSpec``).  With
+    ``f_i = theta^(-2i / rotary_dim)`` and, where the spec has a ``factor``,
+
+        turn(t) = rotary_dim ln(original / (2 pi t)) / (2 ln theta)
+        lo = max(floor(turn(fast)), 0);   hi = min(ceil(turn(slow)), rotary_dim - 1)
+        ramp_i = clamp((i - lo) / max(hi - lo, ramp_floor), 0, 1)
+        f_i <- f_i / factor * ramp_i + f_i (1 - ramp_i);   gain = gain_slope ln(factor) + 1
+
+    the table holds ``gain cos(p f_i), gain sin(p f_i)``, computed in double and rounded once.  ``pairing`` says which
+    columns of a head make a pair: neighbours ``(2i, 2i + 1)`` or halves ``(i, i + rotary_dim / 2)``; the mixer's
+    kernel does the rotation."""
+
+    @classmethod
+    def expected_tensors(cls, spec):
+        return {}
+
+    def __init__(self, spec, weights, rt: Runtime):
+        if spec.rotary_dim % 2 or not 0 < spec.rotary_dim <= spec.head_dim:
+            raise ValueError(f"rotary_dim must be even and within head_dim, got {spec.rotary_dim}")
+        self.spec = spec
+        self.rotary_dim = spec.rotary_dim
+        self.interleaved = bool(spec.interleaved)
+        key = ("scaled", spec.rotary_dim, float(spec.theta), spec.max_positions, spec.factor, float(spec.original),
+               float(spec.fast), float(spec.slow), float(spec.gain_slope), float(spec.ramp_floor), str(rt.device))
+        if key not in _TABLES:
+            _TABLES[key] = self.table(spec).to(torch.float32).to(rt.device).contiguous()
+        self._table = _TABLES[key]
+
+    @staticmethod
+    def frequencies_and_gain(spec):
+        """(float64 [rotary_dim / 2], gain)."""
+        import math
+        dims = spec.rotary_dim
+        pair = torch.arange(dims // 2, dtype=torch.float64)
+        f = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * pair / dims)
+        if spec.factor is None:
+            return f, 1.0
+        if spec.factor <= 0 or spec.original <= 0 or spec.fast <= 0 or spec.slow <= 0 or spec.theta <= 1:
+            raise ValueError("stretched rotation: factor, original, fast and slow must be positive, theta above 1")
+
+        def turn(t):
+            return dims * math.log(spec.original / (2.0 * math.pi * t)) / (2.0 * math.log(spec.theta))
+
+        lo = max(math.floor(turn(spec.fast)), 0)
+        hi = min(math.ceil(turn(spec.slow)), dims - 1)
+        ramp = torch.clamp((pair - lo) / max(hi - lo, spec.ramp_floor), 0.0, 1.0)
+        return f / spec.factor * ramp + f * (1.0 - ramp), spec.gain_slope * math.log(spec.factor) + 1.0
+
+    @classmethod
+    def table(cls, spec):
+        f, gain = cls.frequencies_and_gain(spec)
+        angle = torch.arange(spec.max_positions, dtype=torch.float64)[:, None] * f[None, :]
+        return torch.stack([torch.cos(angle) * gain, torch.sin(angle) * gain], dim=-1)
+
+    def rotation_table(self):
+        """fp32 [max_positions, rotary_dim/2, 2] holding (gain cos, gain sin)."""
+        return self._table

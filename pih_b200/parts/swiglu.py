@@ -7,6 +7,10 @@ rounded to the stream's dtype, ``(g / (1 + exp(-g))) * u`` is computed in
 up as two library products; here their weights are stacked (in blocks of 8
 gate rows and their 8 up rows) so that one product reads the activations
 once and can apply SiLU-mul in its epilogue.
+
+``activation`` "gelu_tanh" makes it ``down( gelu(gate(x)) * up(x) )`` with the tanh form of GELU,
+``z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``: the same stacked product, the activation by its own kernel
+(the products' fused epilogues are SiLU's).
 """
 from __future__ import annotations
 
@@ -28,8 +32,8 @@ class SwiGLU:
                 n["down"]: TensorInfo((spec.hidden, spec.intermediate))}
 
     def __init__(self, spec, weights, rt: Runtime):
-        if spec.activation != "silu":
-            raise ValueError(f"SwiGLU supports activation 'silu', got {spec.activation!r}")
+        if spec.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"the gated feed-forward supports activation 'silu' or 'gelu_tanh', got {spec.activation!r}")
         self.spec = spec
         self.rt = rt
         n = spec.names
@@ -44,6 +48,8 @@ class SwiGLU:
 
     def forward(self, x):
         ops = self.rt.ops
+        if self.spec.activation != "silu":
+            return ops.linear(ops.act_mul(ops.linear(x, self.w_gate_up), self.interleave, self.spec.activation), self.w_down)
         act = None
         if self.interleave == 8 and x.shape[0] <= getattr(ops, "skinny_max_rows", 0) and hasattr(ops, "linear_skinny"):
             act = ops.linear_skinny(x, self.w_gate_up, swiglu=True)      # few rows: SiLU-mul in the product's epilogue
@@ -57,6 +63,8 @@ class SwiGLU:
         gate-up product where the kernels can; returns ``(h', y)`` — or ``(h' + y, None)`` when the down product
         added the residual itself."""
         ops = self.rt.ops
+        if self.spec.activation != "silu":
+            return h, self.forward(norm.add_forward(h, delta))
         h, act = ops.norm_linear(h, delta, norm.weight, norm.spec.eps, self.w_gate_up,
                                  swiglu_interleave=self.interleave)
         if hasattr(ops, "linear_add"):

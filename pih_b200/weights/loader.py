@@ -73,6 +73,16 @@ def _open_files(model_dir: str) -> Dict[str, SafetensorsFile]:
     raise FileNotFoundError(f"{model_dir}: neither model.safetensors nor model.safetensors.index.json")
 
 
+def tensor_shapes(model_dir: str) -> Dict[str, Tuple[int, ...]]:
+    """``{name: shape}`` of every tensor in the folder's weight files (headers only)."""
+    files = _open_files(model_dir)
+    try:
+        return {name: tuple(f.records[name].shape) for name, f in files.items()}
+    finally:
+        for f in set(files.values()):
+            f.close()
+
+
 def load_weights(model_dir: str, expected: Mapping[str, Tuple[int, ...]],
                  optional: Mapping[str, Tuple[int, ...]] = ()) -> Dict[str, torch.Tensor]:
     """Return ``{name: cpu tensor}`` for exactly the ``expected`` names.

@@ -411,3 +411,107 @@ class FakeOps:
                 out[t, h] = a[0] - lam * a[1]
         out = out / torch.sqrt((out * out).mean(-1, keepdim=True) + norm_eps) * out_scale
         return out.reshape(T, heads * value_dim).to(qkv.dtype)
+
+    # -- several residual streams, attention over a window with a sink ----------------------------------------------
+    def act_mul(self, gate_up, interleave=None, activation="silu"):
+        if activation == "silu":
+            return self.silu_mul(gate_up, interleave)
+        assert activation == "gelu_tanh"
+        inter = gate_up.shape[1] // 2
+        il = interleave or inter
+        blocks = gate_up.reshape(gate_up.shape[0], inter // il, 2, il).float()
+        g, u = blocks[:, :, 0, :].reshape(-1, inter), blocks[:, :, 1, :].reshape(-1, inter)
+        return (0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3))) * u).to(gate_up.dtype)
+
+    def embed_positions(self, table, places, ids, positions, streams=1, out_dtype=torch.float32):
+        x = table[ids.long()].float()
+        if places is not None:
+            x = x + places[positions.long()].float()
+        return x[:, None, :].repeat(1, streams, 1).to(out_dtype).contiguous()
+
+    def hyper_stream(self, x, y, *, mix=None, spread=None, collect=None, weight=None, eps=0.0, rows=None, out_dtype=None):
+        assert x.dtype == torch.float32
+        v = x if rows is None else x[rows.long()]
+        if y is not None:
+            yy = (y if rows is None else y[rows.long()]).float()
+            v = torch.einsum("st,nsw->ntw", mix, v) + spread[None, :, None] * yy[:, None, :]
+            if rows is None:
+                x.copy_(v)
+        if collect is None:
+            return None
+        u = torch.einsum("t,ntw->nw", collect, v)
+        if weight is not None:
+            u = u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * weight
+        return u.to(out_dtype or torch.float32)
+
+    def window_qk_prepare(self, src, *, q_norm, k_norm, eps, rope_table, rotary_dim, interleaved, positions, slot_mapping,
+                          cache, heads, kv_heads, key_dim, value_dim, values_from_keys):
+        T = src.shape[0]
+        nq, nk, nv = heads * key_dim, kv_heads * key_dim, kv_heads * value_dim
+
+        def prepared(x, w):
+            x = x.float()
+            if w is not None:
+                x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * w
+            x = x.view(T, -1, key_dim).clone()
+            if rope_table is not None:
+                cs = rope_table[positions.long()]                       # [T, rot / 2, 2]
+                c, s = cs[..., 0][:, None, :], cs[..., 1][:, None, :]
+                if interleaved:
+                    a, b = x[..., 0:rotary_dim:2].clone(), x[..., 1:rotary_dim:2].clone()
+                    x[..., 0:rotary_dim:2], x[..., 1:rotary_dim:2] = a * c - b * s, b * c + a * s
+                else:
+                    half = rotary_dim // 2
+                    a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
+                    x[..., :half], x[..., half:rotary_dim] = a * c - b * s, b * c + a * s
+            return x.reshape(T, -1)
+
+        q = prepared(src[:, :nq], q_norm).to(src.dtype)
+        k = prepared(src[:, nq:nq + nk], k_norm).to(src.dtype)
+        v = src[:, nq:nq + nk] if values_from_keys else src[:, nq + nk:nq + nk + nv]
+        flat = cache.view(-1, cache.shape[-1])
+        for t, slot in enumerate(slot_mapping.tolist()):
+            if slot == -2:
+                continue
+            assert slot >= 0
+            flat[slot, :nk] = k[t]
+            flat[slot, nk:] = v[t]
+        return q
+
+    def window_attention(self, q, *, cache, block_table, step, scale, window, keep_first, softcap, bias, sink, gate, heads,
+                         kv_heads, key_dim, value_dim):
+        T = q.shape[0]
+        page_size = cache.shape[1]
+        nk = kv_heads * key_dim
+        out = torch.zeros(T, heads, value_dim)
+        for t in range(T):
+            r = int(step.request_of_row[t])
+            if r < 0:
+                continue
+            p = int(step.positions[t])
+            js = torch.arange(0, p + 1)
+            if window:
+                js = js[(p - js < window) | (js < keep_first)]
+            pages = block_table[r, (js // page_size).long()].long()
+            if not (pages >= 0).all():
+                self._report(2)
+                pages = pages.clamp(min=0)
+            C = cache[pages, (js % page_size).long()].float()
+            K = C[:, :nk].view(-1, kv_heads, key_dim)
+            V = C[:, nk:].view(-1, kv_heads, value_dim)
+            qq = q[t].float().view(heads, key_dim)
+            for h in range(heads):
+                g = h // (heads // kv_heads)
+                s = (K[:, g] @ qq[h]) * scale
+                if softcap:
+                    s = softcap * torch.tanh(s / softcap)
+                if bias is not None:
+                    s = s + bias[h, (p - js).clamp(max=bias.shape[1] - 1)]
+                m = s.max() if sink is None else torch.maximum(s.max(), sink[h])
+                e = torch.exp(s - m)
+                den = e.sum() + (torch.exp(sink[h] - m) if sink is not None else 0.0)
+                o = (e / den) @ V[:, g]
+                if gate is not None:
+                    o = o * torch.sigmoid(gate[t, h].float())
+                out[t, h] = o
+        return out.reshape(T, heads * value_dim).to(q.dtype)
