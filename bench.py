@@ -335,6 +335,29 @@ def _tuganex_config(width: int, layers: int, kinds=("attention", "retention"), m
     return {"architecture": "Tuganex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": out}
 
 
+def _pegopel_config(width: int, layers: int, kinds=("attention", "attention_2"), window: int = 1024, keep_first: int = 64,
+                    mlp: bool = True, streams: int = 2, loop=None, vocab: int = 32768):
+    """Layer sizes that resemble a real model's at this width: 128-wide heads, half as many key/value heads (the dense
+    decoder's), windows of ``window`` keys (beyond the context: every key is seen, as in the dense decoder), four-tap
+    convolutions and a bias table of 32 rows on the one mixer; a stretched rotation over half of each head, capped
+    scores, ``keep_first`` kept tokens and the head gates on the other; a feed-forward of three times the width; two
+    residual streams."""
+    heads = width // 128 * 2
+    common = {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "scale": 128 ** -0.5}
+    mixers = {"attention": dict(common, conv=4, bias_max=float(2 * window), bias_rows=32, mask={"size": window}),
+              "attention_2": dict(common, softcap=30.0, mask={"size": window, "keep_first": keep_first},
+                                  rot={"dims": 64, "base": 1e6, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0,
+                                                                            "slow": 1.0}})}
+    out = {"architecture": "Pegopel", "vocab": vocab, "width": width, "max_positions": 8192, "norm": {"eps": 1e-6},
+           "layers": [{"type": kinds[i % len(kinds)], "mixer": mixers[kinds[i % len(kinds)]],
+                       "mlp": {"kind": "dense", "ff": 3 * width} if mlp else None} for i in range(layers)]}
+    if streams:
+        out["streams"] = streams
+    if loop is not None:
+        out["loop"] = {"start": loop[0], "stop": loop[1], "times": loop[2]}
+    return out
+
+
 def _dense_config(width: int, layers: int, vocab: int = 32768):
     return dict(QWEN3_0_6B, hidden_size=width, intermediate_size=3 * width, num_hidden_layers=layers,
                 num_attention_heads=width // 128 * 2, num_key_value_heads=width // 128, head_dim=128, vocab_size=vocab,
@@ -406,7 +429,21 @@ def design_run(args) -> int:
     batch, context, prompt, steps = args.batch, CONTEXT, PREFILL_TOKENS, max(8, args.steps // 4)
     with ClockSampler() as clocks:
         for width in (1024, 2048):
-            if args.design == "tuganex":
+            if args.design == "pegopel":
+                # the design beside the models nearest to it (softmax attention over pages and a gated dense
+                # feed-forward), and each of its mixers alone, seeing every key, beside the other attentions alone
+                cases = [("pegopel", _pegopel_config(width, 8)), ("pegopel, every key seen", _pegopel_config(width, 8, window=8192)),
+                         ("dense", _dense_config(width, 8)),
+                         ("tuganex attention, dense feed-forward", _tuganex_config(width, 8, kinds=("attention",), mlps=("dense",)))]
+                if width == 1024:
+                    cases += [(f"pegopel {k} x4, no feed-forward, every key seen",
+                               _pegopel_config(width, 4, kinds=(k,), window=8192, mlp=False)) for k in ("attention", "attention_2")]
+                    cases += [(f"pegopel {k} x4, no feed-forward", _pegopel_config(width, 4, kinds=(k,), mlp=False))
+                              for k in ("attention", "attention_2")]
+                    cases += [("tuganex attention x4, no feed-forward", _tuganex_config(width, 4, kinds=("attention",), mlps=None)),
+                              ("pegopel attention x4, one stream", _pegopel_config(width, 4, kinds=("attention",), streams=0)),
+                              ("pegopel 2 layers run 4 times", _pegopel_config(width, 4, loop=(1, 3, 4)))]
+            elif args.design == "tuganex":
                 # the design beside the two models that are nearest to it (mixers with a state and routed experts; a
                 # softmax attention and a dense feed-forward), and each of its kinds of layer alone beside its like
                 cases = [("tuganex", _tuganex_config(width, 8, share_from=6)), ("rigotar", _rigotar_config(width, 8)),
@@ -461,7 +498,7 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
-    ap.add_argument("--design", default=None, choices=["rigotar", "tuganex"],
+    ap.add_argument("--design", default=None, choices=["rigotar", "tuganex", "pegopel"],
                     help="instead of the recorded workload: this design's prompt and decode throughput beside the dense decoder's")
     ap.add_argument("--plain-launches", action="store_true",
                     help="launch kernels fully serialised instead of with programmatic dependent launch")

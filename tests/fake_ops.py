@@ -181,7 +181,8 @@ class FakeOps:
         taps = w.shape[1]
         out = torch.zeros(T, C, dtype=x.dtype)
         for lo, hi, slot in self._requests(step):
-            hist = state[slot, state_offset:state_offset + (taps - 1) * C].view(taps - 1, C)
+            hist = (state[slot, state_offset:state_offset + (taps - 1) * C].view(taps - 1, C) if taps > 1
+                    else torch.zeros(0, C))                     # a single tap keeps no history
             xin = x[lo:hi].float() + (in_bias if in_bias is not None else 0.0)
             seq = torch.cat([hist, xin], dim=0)
             acc = torch.zeros(hi - lo, C)
