@@ -12,6 +12,10 @@ __device__ __forceinline__ void copy_async_16(void* smem, const void* gmem) {
   const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
 }
+__device__ __forceinline__ void copy_async_4(void* smem, const void* gmem) {
+  const uint32_t s = static_cast<uint32_t>(__cvta_generic_to_shared(smem));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(s), "l"(gmem));
+}
 __device__ __forceinline__ void copy_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
 template <int N> __device__ __forceinline__ void copy_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
@@ -39,9 +43,17 @@ __device__ __forceinline__ uint32_t pack(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<uint32_t*>(&v);
 }
-// the part of (lo, hi) that their bf16 roundings leave out, as bf16
-__device__ __forceinline__ uint32_t pack_remainder(float lo, float hi) {
-  return pack(lo - __bfloat162float(__float2bfloat16_rn(lo)), hi - __bfloat162float(__float2bfloat16_rn(hi)));
+// the part of (lo, hi) that their bf16 roundings ``packed`` (= pack(lo, hi)) leave out, as bf16: a bf16 is the upper
+// half of a float, so the roundings come back by a shift and a mask
+__device__ __forceinline__ uint32_t pack_remainder(float lo, float hi, uint32_t packed) {
+  return pack(lo - __uint_as_float(packed << 16), hi - __uint_as_float(packed & 0xffff0000u));
+}
+__device__ __forceinline__ uint32_t pack_remainder(float lo, float hi) { return pack_remainder(lo, hi, pack(lo, hi)); }
+// 2^x by the special-function unit (results below the smallest normal number are zero; 2^-inf = 0)
+__device__ __forceinline__ float exp2_fast(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+  return y;
 }
 
 }  // namespace mma

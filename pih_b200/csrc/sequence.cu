@@ -102,18 +102,30 @@ causal_conv_kernel(const T* __restrict__ x, long long ldx, const T* __restrict__
   for (int j = 0; j < kMaxTaps; ++j) wr[j] = j < taps ? to_float<T>(w[static_cast<long long>(c) * taps + j]) : 0.0f;
   const float ib = in_bias != nullptr ? in_bias[c] : 0.0f;
   const float ob = out_bias != nullptr ? out_bias[c] : 0.0f;
-  const int t_end = min(n, t_first + kConvRows);
-  for (int t = t_first + threadIdx.y; t < t_end; t += blockDim.y) {
+  // a token lane takes a run of consecutive rows and keeps the last taps inputs in registers: every input is read once
+  const int per = kConvRows / static_cast<int>(blockDim.y);
+  const int t0 = t_first + static_cast<int>(threadIdx.y) * per, t1 = min(n, t0 + per);
+  if (t0 >= t1) return;
+  auto input = [&](int s) {
+    return s >= 0 ? to_float<T>(x[static_cast<long long>(lo + s) * ldx + c]) + ib
+                  : st[static_cast<long long>(hist_n + s) * channels + c];
+  };
+  float held[kMaxTaps];                                       // held[j] = in(t - hist_n + j), j < taps
+#pragma unroll
+  for (int j = 0; j < kMaxTaps; ++j) held[j] = (j + 1 < taps) ? input(t0 - hist_n + j) : 0.0f;
+#pragma unroll 4
+  for (int t = t0; t < t1; ++t) {
+    const float newest = input(t);
     float acc = 0.0f;
 #pragma unroll
     for (int j = 0; j < kMaxTaps; ++j) {
       if (j < taps) {
-        const int s = t - hist_n + j;
-        const float v = s >= 0 ? to_float<T>(x[static_cast<long long>(lo + s) * ldx + c]) + ib
-                               : st[static_cast<long long>(hist_n + s) * channels + c];
+        const float v = j + 1 == taps ? newest : held[j];
         acc = fmaf(wr[j], v, acc);
       }
     }
+#pragma unroll
+    for (int j = 0; j + 1 < kMaxTaps; ++j) held[j] = j + 2 == taps ? newest : held[j + 1];
     acc += ob;
     if (activation == 1) acc = acc / (1.0f + expf(-acc));
     out[static_cast<long long>(lo + t) * ldo + c] = from_float<T>(acc);

@@ -53,8 +53,32 @@ __device__ __forceinline__ float finish_score(float dot, const WindowRule& rule,
   return s;
 }
 
-// One block a row.  src [rows, ld]: q [heads x dim] | k [kv_heads x dim] | v [kv_heads x vdim] (v absent with
-// values_from_keys).  table: fp32 [max_positions][rot / 2][2] (cos, sin) or null.
+// WORDS (1, 2 or 4) 32-bit words from an address that is a multiple of their size, as one load; and element i of type T
+// out of such words.
+template <int WORDS>
+__device__ __forceinline__ void load_words(uint32_t (&w)[WORDS], const void* src) {
+  static_assert(WORDS == 1 || WORDS == 2 || WORDS == 4, "one load");
+  if constexpr (WORDS == 4) {
+    const uint4 r = *reinterpret_cast<const uint4*>(src);
+    w[0] = r.x; w[1] = r.y; w[2] = r.z; w[3] = r.w;
+  } else if constexpr (WORDS == 2) {
+    const uint2 r = *reinterpret_cast<const uint2*>(src);
+    w[0] = r.x; w[1] = r.y;
+  } else {
+    w[0] = *reinterpret_cast<const uint32_t*>(src);
+  }
+}
+template <typename T, int WORDS>
+__device__ __forceinline__ float element_of_words(const uint32_t (&w)[WORDS], int i) {
+  if constexpr (sizeof(T) == 4) return __uint_as_float(w[i]);
+  else return __uint_as_float((i & 1) ? (w[i >> 1] & 0xffff0000u) : (w[i >> 1] << 16));     // bf16: the upper half of a float
+}
+
+// A block is a (row, part): part 0 the row's q, part 1 its k, part 2 its v.  src [rows, ld]: q [heads x dim] |
+// k [kv_heads x dim] | v [kv_heads x vdim] (v absent with values_from_keys).  table: fp32 [max_positions][rot / 2][2]
+// (cos, sin) or null.  Where the sizes keep 16-byte pieces aligned and inside a head (and the rotation pairs
+// neighbours), a thread keeps its pieces in registers between the sum of squares and the writing; else element by
+// element.
 template <typename T>
 __global__ void __launch_bounds__(256)
 window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict__ q_out, const float* __restrict__ q_norm,
@@ -62,67 +86,122 @@ window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict_
                          int interleaved, int max_positions, const int* __restrict__ positions,
                          const int* __restrict__ slot_mapping, T* __restrict__ cache, long long cache_slots, int heads,
                          int kv_heads, int dim, int vdim, int values_from_keys, uint32_t* __restrict__ error) {
+  constexpr int V = 16 / static_cast<int>(sizeof(T));         // elements a piece
+  constexpr int kWords = 4;
+  constexpr int kHeld = 2;                                     // pieces a thread keeps
   __shared__ float scratch[33];
   wait_for_prior_kernels();
   launch_dependents();
   const long long row = blockIdx.x;
+  const int part = blockIdx.y;
   const int nq = heads * dim, nk = kv_heads * dim, nv = kv_heads * vdim;
   const long long width = nk + nv;
   int slot = slot_mapping[row];
   if (slot != kPaddingSlot && (slot < 0 || slot >= cache_slots)) {
-    if (threadIdx.x == 0) publish_error(error, kRowWithoutPage);
+    if (threadIdx.x == 0 && part == 0) publish_error(error, kRowWithoutPage);
     slot = kPaddingSlot;
+  }
+  const T* x = src + row * ld;
+  const bool aligned = ld % V == 0 && nq % V == 0 && nk % V == 0 && width % V == 0;
+  if (part == 2) {                                             // the values: a copy
+    if (slot < 0) return;
+    const T* v = values_from_keys ? x + nq : x + nq + nk;
+    T* dst = cache + slot * width + nk;
+    if (aligned && nv % V == 0) {
+      for (int e = threadIdx.x * V; e < nv; e += blockDim.x * V)
+        *reinterpret_cast<uint4*>(dst + e) = *reinterpret_cast<const uint4*>(v + e);
+    } else {
+      for (int e = threadIdx.x; e < nv; e += blockDim.x) dst[e] = v[e];
+    }
+    return;
   }
   int pos = positions[row];
   if (table != nullptr && (pos < 0 || pos >= max_positions)) {
-    if (threadIdx.x == 0) publish_error(error, kBadPosition);
+    if (threadIdx.x == 0 && part == 0) publish_error(error, kBadPosition);
     pos = 0;
   }
-  const T* x = src + row * ld;
   const float* cs = table != nullptr ? table + static_cast<long long>(pos) * rot : nullptr;   // (rot / 2) pairs of 2
   const int half = rot >> 1;
-  for (int part = 0; part < 2; ++part) {
-    const T* xp = part == 0 ? x : x + nq;
-    const int n = part == 0 ? nq : nk;
-    const float* w = part == 0 ? q_norm : k_norm;
+  const T* xp = part == 0 ? x : x + nq;
+  const int n = part == 0 ? nq : nk;
+  const float* w = part == 0 ? q_norm : k_norm;
+  T* dst = part == 0 ? q_out + row * nq : (slot >= 0 ? cache + slot * width : nullptr);
+  if (dst == nullptr) return;
+  const bool pieces = aligned && dim % V == 0 && (cs == nullptr || (interleaved && rot % V == 0)) &&
+                      n <= static_cast<int>(blockDim.x) * V * kHeld;
+  if (pieces) {
+    float held[kHeld][V];
+    float ss = 0.0f;
+#pragma unroll
+    for (int u = 0; u < kHeld; ++u) {
+      const int e = (threadIdx.x + u * blockDim.x) * V;
+      uint32_t raw[kWords] = {0u, 0u, 0u, 0u};
+      if (e < n) load_words<kWords>(raw, xp + e);
+#pragma unroll
+      for (int i = 0; i < V; ++i) {
+        held[u][i] = element_of_words<T, kWords>(raw, i);
+        ss = fmaf(held[u][i], held[u][i], ss);
+      }
+    }
     float inv = 1.0f;
     if (w != nullptr) {
-      float ss = 0.0f;
-      for (int e = threadIdx.x; e < n; e += blockDim.x) {
-        const float v = to_float<T>(xp[e]);
-        ss = fmaf(v, v, ss);
-      }
       ss = block_sum(ss, scratch);
       inv = 1.0f / sqrtf(ss / static_cast<float>(n) + eps);
     }
-    T* dst = part == 0 ? q_out + row * nq : (slot >= 0 ? cache + slot * width : nullptr);
-    if (dst == nullptr) continue;
-    for (int e = threadIdx.x; e < n; e += blockDim.x) {
-      const int c = e % dim;                                   // column within the head
-      float o = to_float<T>(xp[e]);
-      if (w != nullptr) o = o * inv * w[e];
+#pragma unroll
+    for (int u = 0; u < kHeld; ++u) {
+      const int e = (threadIdx.x + u * blockDim.x) * V;
+      if (e >= n) continue;
+      float o[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) o[i] = w != nullptr ? held[u][i] * inv * w[e + i] : held[u][i];
+      const int c = e % dim;                                   // the piece lies inside a head, and inside or outside the rotation
       if (cs != nullptr && c < rot) {
-        int pair, other;
-        bool first;                                            // whether e is the first number of its pair
-        if (interleaved) { pair = c >> 1; first = (c & 1) == 0; other = first ? e + 1 : e - 1; }
-        else { pair = c < half ? c : c - half; first = c < half; other = first ? e + half : e - half; }
-        float p = to_float<T>(xp[other]);
-        if (w != nullptr) p = p * inv * w[other];
-        const float cosine = cs[2 * pair], sine = cs[2 * pair + 1];
-        o = first ? o * cosine - p * sine : o * cosine + p * sine;
+#pragma unroll
+        for (int i = 0; i < V; i += 2) {
+          const float cosine = cs[c + i], sine = cs[c + i + 1];   // pair (c + i) / 2
+          const float a = o[i], b = o[i + 1];
+          o[i] = a * cosine - b * sine;
+          o[i + 1] = b * cosine + a * sine;
+        }
       }
-      dst[e] = from_float<T>(o);
+      T out[V];
+#pragma unroll
+      for (int i = 0; i < V; ++i) out[i] = from_float<T>(o[i]);
+      *reinterpret_cast<uint4*>(dst + e) = *reinterpret_cast<const uint4*>(out);
     }
+    return;
   }
-  if (slot >= 0) {
-    const T* v = values_from_keys ? x + nq : x + nq + nk;
-    T* dst = cache + slot * width + nk;
-    for (int e = threadIdx.x; e < nv; e += blockDim.x) dst[e] = v[e];
+  float inv = 1.0f;
+  if (w != nullptr) {
+    float ss = 0.0f;
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+      const float v = to_float<T>(xp[e]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    inv = 1.0f / sqrtf(ss / static_cast<float>(n) + eps);
+  }
+  for (int e = threadIdx.x; e < n; e += blockDim.x) {
+    const int c = e % dim;                                     // column within the head
+    float o = to_float<T>(xp[e]);
+    if (w != nullptr) o = o * inv * w[e];
+    if (cs != nullptr && c < rot) {
+      int pair, other;
+      bool first;                                              // whether e is the first number of its pair
+      if (interleaved) { pair = c >> 1; first = (c & 1) == 0; other = first ? e + 1 : e - 1; }
+      else { pair = c < half ? c : c - half; first = c < half; other = first ? e + half : e - half; }
+      float p = to_float<T>(xp[other]);
+      if (w != nullptr) p = p * inv * w[other];
+      const float cosine = cs[2 * pair], sine = cs[2 * pair + 1];
+      o = first ? o * cosine - p * sine : o * cosine + p * sine;
+    }
+    dst[e] = from_float<T>(o);
   }
 }
 
 // The sums of one (row, head) over the keys first .. last (absolute places; chunks of 32 at multiples of 32): a lane a key
-// for the scores, a lane a value column (lane + 32 e) for the sums.  q: 32-bit.
+// for the scores, a lane PL neighbouring value columns (PL lane + e) for the sums.  q: 32-bit.
 template <typename T, int PL>
 __device__ __forceinline__ void window_stretch(const float* q, const T* __restrict__ cache, const int* __restrict__ table,
                                                int first, int last, int pos, int g, int kv_heads, int dim, int vdim,
@@ -143,26 +222,36 @@ __device__ __forceinline__ void window_stretch(const float* q, const T* __restri
     float s = -INFINITY;
     if (at >= 0) {
       const T* k = cache + at + static_cast<long long>(g) * dim;
-      float d = 0.0f;
+      // four sums side by side (column e joins sum e % 4), folded at the end: the chain of dependent additions is a
+      // quarter as long, and both ways of loading add in the same order
+      float d4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
       constexpr int kVec = 16 / sizeof(T);
-      if (dim % kVec == 0 && width % kVec == 0) {             // 16-byte loads; the additions in the same order
-        for (int e0 = 0; e0 < dim; e0 += 4 * kVec) {
-          uint4 r[4];
+      if (dim % kVec == 0 && width % kVec == 0) {             // 16-byte loads
+        for (int e0 = 0; e0 < dim; e0 += 8 * kVec) {
+          uint4 r[8];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) r[u] = *reinterpret_cast<const uint4*>(k + min(e0 + u * kVec, dim - kVec));
+          for (int u = 0; u < 8; ++u) r[u] = *reinterpret_cast<const uint4*>(k + min(e0 + u * kVec, dim - kVec));
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < 8; ++u) {
             const int e = e0 + u * kVec;
             if (e < dim) {
               const T* kk = reinterpret_cast<const T*>(&r[u]);
 #pragma unroll
-              for (int i = 0; i < kVec; ++i) d = fmaf(q[e + i], to_float<T>(kk[i]), d);
+              for (int i = 0; i < kVec; ++i) d4[i & 3] = fmaf(q[e + i], to_float<T>(kk[i]), d4[i & 3]);
             }
           }
         }
       } else {
-        for (int e = 0; e < dim; ++e) d = fmaf(q[e], to_float<T>(k[e]), d);
+        int e = 0;
+        for (; e + 3 < dim; e += 4) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) d4[i] = fmaf(q[e + i], to_float<T>(k[e + i]), d4[i]);
+        }
+#pragma unroll
+        for (int i = 0; i < 3; ++i)
+          if (e + i < dim) d4[i] = fmaf(q[e + i], to_float<T>(k[e + i]), d4[i]);
       }
+      const float d = (d4[0] + d4[1]) + (d4[2] + d4[3]);
       s = finish_score<kExact>(d, rule, bias_of_head, pos - j);
     }
     const float top = fmaxf(m, warp_max(s));
@@ -174,8 +263,13 @@ __device__ __forceinline__ void window_stretch(const float* q, const T* __restri
 #pragma unroll
     for (int e = 0; e < PL; ++e) a[e] *= fix;
     const long long v_at = at >= 0 ? at + static_cast<long long>(kv_heads) * dim + static_cast<long long>(g) * vdim : -1;
-    // the values of kBatch keys are asked for together: shuffles first, then all loads, then the sums in the keys' order
-    constexpr int kBatch = PL <= 4 ? 8 : (PL <= 8 ? 4 : 2);
+    // the values of kBatch keys are asked for together: shuffles first, then all loads, then the sums in the keys' order.
+    // A lane holds the PL neighbouring columns from PL * lane on and loads them in pieces of up to 16 bytes where the
+    // sizes keep every piece aligned.
+    constexpr int kPiece = PL * sizeof(T) <= 16 ? PL : 16 / static_cast<int>(sizeof(T));
+    constexpr int kWords = kPiece * static_cast<int>(sizeof(T)) / 4;
+    constexpr int kBatch = PL <= 4 ? 16 : (PL <= 8 ? 8 : 4);
+    const bool pieces = vdim % kPiece == 0 && width % kPiece == 0 && (static_cast<long long>(kv_heads) * dim) % kPiece == 0;
     for (int j8 = 0; j8 < 32; j8 += kBatch) {
       long long va[kBatch];
       float wgt[kBatch], x[kBatch][PL];
@@ -184,11 +278,30 @@ __device__ __forceinline__ void window_stretch(const float* q, const T* __restri
         va[b] = __shfl_sync(0xffffffffu, v_at, j8 + b);
         wgt[b] = __shfl_sync(0xffffffffu, p, j8 + b);
       }
+      if (pieces) {
+        uint32_t raw[kBatch][PL / kPiece][kWords];
 #pragma unroll
-      for (int b = 0; b < kBatch; ++b) {
-        const T* v = cache + (va[b] >= 0 ? va[b] : 0);
+        for (int b = 0; b < kBatch; ++b) {
+          const T* v = cache + (va[b] >= 0 ? va[b] : 0) + PL * lane;
 #pragma unroll
-        for (int e = 0; e < PL; ++e) x[b][e] = (lane + 32 * e < vdim) ? to_float<T>(v[lane + 32 * e]) : 0.0f;
+          for (int c = 0; c < PL / kPiece; ++c) {
+            if (PL * lane + c * kPiece < vdim) load_words<kWords>(raw[b][c], v + c * kPiece);
+            else
+#pragma unroll
+              for (int i = 0; i < kWords; ++i) raw[b][c][i] = 0u;
+          }
+        }
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b)
+#pragma unroll
+          for (int e = 0; e < PL; ++e) x[b][e] = element_of_words<T, kWords>(raw[b][e / kPiece], e % kPiece);
+      } else {
+#pragma unroll
+        for (int b = 0; b < kBatch; ++b) {
+          const T* v = cache + (va[b] >= 0 ? va[b] : 0) + PL * lane;
+#pragma unroll
+          for (int e = 0; e < PL; ++e) x[b][e] = (PL * lane + e < vdim) ? to_float<T>(v[e]) : 0.0f;
+        }
       }
 #pragma unroll
       for (int b = 0; b < kBatch; ++b) {
@@ -200,7 +313,7 @@ __device__ __forceinline__ void window_stretch(const float* q, const T* __restri
   }
 }
 
-// The sink joins the denominator, the sums are divided, the gate multiplies; a lane holds columns lane + 32 e.
+// The sink joins the denominator, the sums are divided, the gate multiplies; a lane holds columns PL lane + e.
 template <typename T, int PL>
 __device__ __forceinline__ void window_finish(float (&a)[PL], float m, float l, const float* __restrict__ sink, int head,
                                               const T* __restrict__ gate, int vdim, int lane, T* __restrict__ out,
@@ -220,11 +333,11 @@ __device__ __forceinline__ void window_finish(float (&a)[PL], float m, float l, 
   if (gate != nullptr) f *= 1.0f / (1.0f + expf(-to_float<T>(*gate)));
 #pragma unroll
   for (int e = 0; e < PL; ++e)
-    if (lane + 32 * e < vdim) out[lane + 32 * e] = from_float<T>(a[e] * f);
+    if (PL * lane + e < vdim) out[PL * lane + e] = from_float<T>(a[e] * f);
 }
 
 // A warp a (row, head) and a part of its keys.  splits == 1: the whole row, finished here.  More: part blockIdx.y of the
-// keys of rows whose request brings at most small_rows rows, its sums to partial [row][head][split][2 + vdim]: m, l, a.
+// keys of rows whose request brings at most small_rows rows, its sums to partial [row][head][split][2 + 32 PL]: m, l, a (lane by lane).
 template <typename T, int PL>
 __global__ void __launch_bounds__(128)
 window_attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, const T* __restrict__ cache,
@@ -286,11 +399,11 @@ window_attention_generic_kernel(const T* __restrict__ q, T* __restrict__ out, co
                             lane, a, m, l, error);
   }
   if (splits > 1) {
-    float* p = partial + (unit * splits + blockIdx.y) * (2 + vdim);
+    float* p = partial + (unit * splits + blockIdx.y) * (2 + 32 * PL);
     if (lane == 0) { p[0] = m; p[1] = l; }
 #pragma unroll
     for (int e = 0; e < PL; ++e)
-      if (lane + 32 * e < vdim) p[2 + lane + 32 * e] = a[e];
+      p[2 + 32 * e + lane] = a[e];                             // (column PL lane + e; beyond vdim: zero)
     return;
   }
   window_finish<T, PL>(a, m, l, sink, head, gate != nullptr ? gate + row * ld_gate + head : nullptr, vdim, lane, o, error);
@@ -311,10 +424,10 @@ window_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__
   const int row = static_cast<int>(unit / heads), head = static_cast<int>(unit % heads);
   const int req = request_of_row[row];
   if (req < 0 || cu_q[req + 1] - cu_q[req] > small_rows) return;
-  const float* base = partial + unit * splits * (2 + vdim);
+  const float* base = partial + unit * splits * (2 + 32 * PL);
   float pm = -INFINITY, pl = 0.0f;
   if (lane < splits) {
-    const float* p = base + static_cast<long long>(lane) * (2 + vdim);
+    const float* p = base + static_cast<long long>(lane) * (2 + 32 * PL);
     pm = p[0]; pl = p[1];
   }
   const float m = warp_max(pm);
@@ -323,13 +436,13 @@ window_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__
   float a[PL];
 #pragma unroll
   for (int e = 0; e < PL; ++e) a[e] = 0.0f;
-#pragma unroll 4
+#pragma unroll 8
   for (int s = 0; s < splits; ++s) {
-    const float* p = base + static_cast<long long>(s) * (2 + vdim);
+    const float* p = base + static_cast<long long>(s) * (2 + 32 * PL);
     const float d = __shfl_sync(0xffffffffu, f, s);
 #pragma unroll
     for (int e = 0; e < PL; ++e)
-      if (lane + 32 * e < vdim) a[e] = fmaf(p[2 + lane + 32 * e], d, a[e]);
+      a[e] = fmaf(p[2 + 32 * e + lane], d, a[e]);
   }
   window_finish<T, PL>(a, m, l, sink, head, gate != nullptr ? gate + row * ld_gate + head : nullptr, vdim, lane,
                        out + unit * vdim, error);
@@ -359,11 +472,13 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
   bf16* Ks = Qs + 64 * QLD;                                   // [2][64][QLD]
   bf16* Vs = Ks + 2 * 64 * QLD;                               // [2][64][VLD]
   __shared__ int tile_info[2];
+  __shared__ float bias_s[2][128];                            // the bias of a key tile by (row - key) + 63 of the block
   wait_for_prior_kernels();
   launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) {
-    int t = blockIdx.x, found = -1, at = 0;
+    // the last tiles of a request have the most keys: they start first, so that the short ones fill the end
+    int t = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x), found = -1, at = 0;
     for (int r = 0; r < requests; ++r) {
       const int n = cu_q[r + 1] - cu_q[r];
       if (n <= small_rows) continue;
@@ -388,6 +503,7 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
   const int kept = min(rule.keep_first, key_first);           // kept keys that lie before the first row's window
   const float* bias_of_head = rule.bias != nullptr ? rule.bias + static_cast<long long>(head) * rule.distances : nullptr;
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
   for (int c = tid; c < 64 * QC; c += 128) {
     const int rr = c / QC, col = (c % QC) * 8;
@@ -402,9 +518,10 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
     bf16* vb = Vs + (buf * 64 + key) * VLD;
     long long at = -1;
     if (j <= key_last && (j >= key_first || j < kept)) {
-      const int page = table[j / page_size];
+      const int page = table[page_shift >= 0 ? j >> page_shift : j / page_size];
+      const int offset = page_shift >= 0 ? j & (page_size - 1) : j % page_size;
       if (page < 0 || page >= num_pages) publish_error(error, kRowWithoutPage);
-      else at = (static_cast<long long>(page) * page_size + j % page_size) * width;
+      else at = (static_cast<long long>(page) * page_size + offset) * width;
     }
     const bf16* ksrc = cache + at + static_cast<long long>(g) * dim;
     const bf16* vsrc = cache + at + static_cast<long long>(kv_heads) * dim + static_cast<long long>(g) * vdim;
@@ -420,6 +537,8 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
         else *reinterpret_cast<uint4*>(vb + col) = zero;
       }
     }
+    if (bias_of_head != nullptr && tid < 127)                 // distance (pos0 + row) - (j0 + key), row - key = tid - 63
+      mma::copy_async_4(&bias_s[buf][tid], bias_of_head + min(max(pos0 - j0 + tid - 63, 0), rule.distances - 1));
     mma::copy_async_commit();
   };
   // the tiles in the order they are visited: those of the kept keys that end before the window's first tile, then the window's
@@ -440,57 +559,85 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
   for (int n = 0; n < VDIM / 8; ++n) O[n][0] = O[n][1] = O[n][2] = O[n][3] = 0.0f;
   for (int v = 0; v < visits; ++v) {
     const int buf = v & 1;
-    if (v + 1 < visits) {
-      load_keys(buf ^ 1, tile_of(v + 1) * 64);
-      mma::copy_async_wait<1>();
-    } else {
-      mma::copy_async_wait<0>();
-    }
+    mma::copy_async_wait<0>();
     __syncthreads();
     const int j0 = tile_of(v) * 64;
     // the warp's rows see something of this tile: a key of their windows, or a kept key
     const bool any = wr0 < nrows && j0 <= warp_last &&
                      (rule.window <= 0 || j0 + 63 > warp_first - rule.window || j0 < rule.keep_first);
+    const bf16* kb = Ks + buf * 64 * QLD;
+    const bf16* vb = Vs + buf * 64 * VLD;
+    float S[8][4];
     if (any) {
-      const bf16* kb = Ks + buf * 64 * QLD;
-      const bf16* vb = Vs + buf * 64 * VLD;
-      float S[8][4];
 #pragma unroll
       for (int n = 0; n < 8; ++n) S[n][0] = S[n][1] = S[n][2] = S[n][3] = 0.0f;
+      {
+        // the fragments of step kk + 1 are asked for before the products of step kk: a load is never waited for
+        uint32_t a[2][4], b[2][4][4];
+        auto fetch = [&](int kk, int f) {
+          mma::load_matrices(a[f], Qs + (wr0 + (lane & 15)) * QLD + kk * 16 + (lane >> 4) * 8);
 #pragma unroll
-      for (int kk = 0; kk < DIM / 16; ++kk) {
-        uint32_t a[4];
-        mma::load_matrices(a, Qs + (wr0 + (lane & 15)) * QLD + kk * 16 + (lane >> 4) * 8);
+          for (int np = 0; np < 4; ++np)
+            mma::load_matrices(b[f][np], kb + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * QLD + kk * 16 + ((lane >> 3) & 1) * 8);
+        };
+        fetch(0, 0);
 #pragma unroll
-        for (int np = 0; np < 4; ++np) {
-          uint32_t b[4];
-          mma::load_matrices(b, kb + (np * 16 + (lane >> 4) * 8 + (lane & 7)) * QLD + kk * 16 + ((lane >> 3) & 1) * 8);
-          mma::multiply_add(S[2 * np], a, b[0], b[1]);
-          mma::multiply_add(S[2 * np + 1], a, b[2], b[3]);
+        for (int kk = 0; kk < DIM / 16; ++kk) {
+          if (kk + 1 < DIM / 16) fetch(kk + 1, (kk + 1) & 1);
+#pragma unroll
+          for (int np = 0; np < 4; ++np) {
+            mma::multiply_add(S[2 * np], a[kk & 1], b[kk & 1][np][0], b[kk & 1][np][1]);
+            mma::multiply_add(S[2 * np + 1], a[kk & 1], b[kk & 1][np][2], b[kk & 1][np][3]);
+          }
         }
       }
+    }
+    // the next tile is asked for while the tensor cores work on this tile's scores (its buffer was let go of at the end
+    // of the step before)
+    if (v + 1 < visits) load_keys(buf ^ 1, tile_of(v + 1) * 64);
+    if (any) {
       // a tile that every row of the warp sees whole needs no mask
       const bool whole = j0 + 63 <= warp_first && (rule.window <= 0 || j0 > warp_last - rule.window || j0 + 63 < rule.keep_first);
+      const float* bias_t = bias_of_head != nullptr ? bias_s[buf] + 63 : nullptr;
+      const int la = ra - 2 * (lane & 3), lb = rb - 2 * (lane & 3);   // row - key of the thread's first column
       float top_a = -INFINITY, top_b = -INFINITY;
+      auto finish = [&](float dot, int rel) {                  // rel: row - key inside the block's tile
+        float s = dot * rule.scale;
+        if (rule.cap > 0.0f) s = capped<false>(s, rule.cap);
+        if (bias_t != nullptr) s += bias_t[rel];
+        return s * kLog2e;
+      };
+      if (whole) {
 #pragma unroll
-      for (int n = 0; n < 8; ++n) {
+        for (int n = 0; n < 8; ++n) {
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int key = j0 + n * 8 + 2 * (lane & 3) + c;
-          const bool see_a = whole || (key <= pos_a && (rule.window <= 0 || key > pos_a - rule.window || key < rule.keep_first));
-          const bool see_b = whole || (key <= pos_b && (rule.window <= 0 || key > pos_b - rule.window || key < rule.keep_first));
-          float sa, sb;
-          if (plain) {
-            sa = S[n][c] * (rule.scale * kLog2e);
-            sb = S[n][2 + c] * (rule.scale * kLog2e);
-          } else {
-            sa = see_a ? finish_score<false>(S[n][c], rule, bias_of_head, pos_a - key) * kLog2e : 0.0f;
-            sb = see_b ? finish_score<false>(S[n][2 + c], rule, bias_of_head, pos_b - key) * kLog2e : 0.0f;
+          for (int c = 0; c < 2; ++c) {
+            if (plain) {
+              S[n][c] *= rule.scale * kLog2e;
+              S[n][2 + c] *= rule.scale * kLog2e;
+            } else {
+              S[n][c] = finish(S[n][c], la - n * 8 - c);
+              S[n][2 + c] = finish(S[n][2 + c], lb - n * 8 - c);
+            }
+            top_a = fmaxf(top_a, S[n][c]);
+            top_b = fmaxf(top_b, S[n][2 + c]);
           }
-          S[n][c] = see_a ? sa : -INFINITY;
-          S[n][2 + c] = see_b ? sb : -INFINITY;
-          top_a = fmaxf(top_a, S[n][c]);
-          top_b = fmaxf(top_b, S[n][2 + c]);
+        }
+      } else {
+#pragma unroll
+        for (int n = 0; n < 8; ++n) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int key = j0 + n * 8 + 2 * (lane & 3) + c;
+            const bool see_a = key <= pos_a && (rule.window <= 0 || key > pos_a - rule.window || key < rule.keep_first);
+            const bool see_b = key <= pos_b && (rule.window <= 0 || key > pos_b - rule.window || key < rule.keep_first);
+            const float sa = plain ? S[n][c] * (rule.scale * kLog2e) : finish(S[n][c], la - n * 8 - c);
+            const float sb = plain ? S[n][2 + c] * (rule.scale * kLog2e) : finish(S[n][2 + c], lb - n * 8 - c);
+            S[n][c] = see_a ? sa : -INFINITY;
+            S[n][2 + c] = see_b ? sb : -INFINITY;
+            top_a = fmaxf(top_a, S[n][c]);
+            top_b = fmaxf(top_b, S[n][2 + c]);
+          }
         }
       }
       top_a = fmaxf(top_a, __shfl_xor_sync(0xffffffffu, top_a, 1));
@@ -499,16 +646,16 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
       top_b = fmaxf(top_b, __shfl_xor_sync(0xffffffffu, top_b, 2));
       const float new_a = fmaxf(m_a, top_a), new_b = fmaxf(m_b, top_b);
       const float ref_a = new_a == -INFINITY ? 0.0f : new_a, ref_b = new_b == -INFINITY ? 0.0f : new_b;
-      const float fix_a = exp2f(m_a - ref_a), fix_b = exp2f(m_b - ref_b);
+      const float fix_a = mma::exp2_fast(m_a - ref_a), fix_b = mma::exp2_fast(m_b - ref_b);
       m_a = new_a;
       m_b = new_b;
       float sum_a = 0.0f, sum_b = 0.0f;
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
-        S[n][0] = exp2f(S[n][0] - ref_a);
-        S[n][1] = exp2f(S[n][1] - ref_a);
-        S[n][2] = exp2f(S[n][2] - ref_b);
-        S[n][3] = exp2f(S[n][3] - ref_b);
+        S[n][0] = mma::exp2_fast(S[n][0] - ref_a);
+        S[n][1] = mma::exp2_fast(S[n][1] - ref_a);
+        S[n][2] = mma::exp2_fast(S[n][2] - ref_b);
+        S[n][3] = mma::exp2_fast(S[n][3] - ref_b);
         sum_a += S[n][0] + S[n][1];
         sum_b += S[n][2] + S[n][3];
       }
@@ -521,25 +668,44 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
         O[n][2] *= fix_b;
         O[n][3] *= fix_b;
       }
+      {
+        // 16 keys by 64 value columns a step: the values of the next step are asked for before this step's products;
+        // the eight products with the roundings come before the eight with the remainders, so that none waits for
+        // the one before it
+        constexpr int kGroups = VDIM / 64, kSteps = 4 * kGroups;
+        uint32_t b[2][4][4];
+        auto fetch = [&](int t, int f) {
+          const int kk = t / kGroups, v0 = (t % kGroups) * 4;
 #pragma unroll
-      for (int kk = 0; kk < 4; ++kk) {                        // 16 keys a step
+          for (int u = 0; u < 4; ++u)
+            mma::load_matrices_transposed(b[f][u], vb + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VLD + (v0 + u) * 16 + (lane >> 4) * 8);
+        };
+        fetch(0, 0);
         uint32_t hi[4], lo[4];
-        hi[0] = mma::pack(S[2 * kk][0], S[2 * kk][1]);
-        hi[1] = mma::pack(S[2 * kk][2], S[2 * kk][3]);
-        hi[2] = mma::pack(S[2 * kk + 1][0], S[2 * kk + 1][1]);
-        hi[3] = mma::pack(S[2 * kk + 1][2], S[2 * kk + 1][3]);
-        lo[0] = mma::pack_remainder(S[2 * kk][0], S[2 * kk][1]);
-        lo[1] = mma::pack_remainder(S[2 * kk][2], S[2 * kk][3]);
-        lo[2] = mma::pack_remainder(S[2 * kk + 1][0], S[2 * kk + 1][1]);
-        lo[3] = mma::pack_remainder(S[2 * kk + 1][2], S[2 * kk + 1][3]);
 #pragma unroll
-        for (int vp = 0; vp < VDIM / 16; ++vp) {
-          uint32_t b[4];
-          mma::load_matrices_transposed(b, vb + (kk * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * VLD + vp * 16 + (lane >> 4) * 8);
-          mma::multiply_add(O[2 * vp], hi, b[0], b[1]);
-          mma::multiply_add(O[2 * vp + 1], hi, b[2], b[3]);
-          mma::multiply_add(O[2 * vp], lo, b[0], b[1]);
-          mma::multiply_add(O[2 * vp + 1], lo, b[2], b[3]);
+        for (int t = 0; t < kSteps; ++t) {
+          const int kk = t / kGroups, v0 = (t % kGroups) * 4;
+          if (t + 1 < kSteps) fetch(t + 1, (t + 1) & 1);
+          if (t % kGroups == 0) {
+            hi[0] = mma::pack(S[2 * kk][0], S[2 * kk][1]);
+            hi[1] = mma::pack(S[2 * kk][2], S[2 * kk][3]);
+            hi[2] = mma::pack(S[2 * kk + 1][0], S[2 * kk + 1][1]);
+            hi[3] = mma::pack(S[2 * kk + 1][2], S[2 * kk + 1][3]);
+            lo[0] = mma::pack_remainder(S[2 * kk][0], S[2 * kk][1], hi[0]);
+            lo[1] = mma::pack_remainder(S[2 * kk][2], S[2 * kk][3], hi[1]);
+            lo[2] = mma::pack_remainder(S[2 * kk + 1][0], S[2 * kk + 1][1], hi[2]);
+            lo[3] = mma::pack_remainder(S[2 * kk + 1][2], S[2 * kk + 1][3], hi[3]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            mma::multiply_add(O[2 * (v0 + u)], hi, b[t & 1][u][0], b[t & 1][u][1]);
+            mma::multiply_add(O[2 * (v0 + u) + 1], hi, b[t & 1][u][2], b[t & 1][u][3]);
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            mma::multiply_add(O[2 * (v0 + u)], lo, b[t & 1][u][0], b[t & 1][u][1]);
+            mma::multiply_add(O[2 * (v0 + u) + 1], lo, b[t & 1][u][2], b[t & 1][u][3]);
+          }
         }
       }
     }
@@ -599,7 +765,7 @@ extern "C" int pih_window_qk_prepare(int dtype, const void* src, long long ld, v
   const long long slots = static_cast<long long>(num_pages) * page_size;
   const int threads = heads * dim >= 1024 ? 256 : 128;
 #define PIH_WQK(T)                                                                                                     \
-  launch_kernel(window_qk_prepare_kernel<T>, dim3(rows), dim3(threads), 0, s, static_cast<const T*>(src), ld,          \
+  launch_kernel(window_qk_prepare_kernel<T>, dim3(rows, 3), dim3(threads), 0, s, static_cast<const T*>(src), ld,          \
                 static_cast<T*>(q_out), static_cast<const float*>(q_norm), static_cast<const float*>(k_norm), eps,     \
                 static_cast<const float*>(rot > 0 ? table : nullptr), rot, interleaved, max_positions,                 \
                 static_cast<const int*>(positions), static_cast<const int*>(slot_mapping), static_cast<T*>(cache), slots, \
@@ -642,7 +808,7 @@ extern "C" int pih_window_attention_tile_takes(int dim, int vdim) {
 // [heads, distances] or null; sink fp32 [heads] or null; gate [rows, ld_gate] of the compute dtype (column h: head h's
 // logit) or null.  ``tile`` (bf16 only, sizes that pih_window_attention_tile_takes): requests of more than 16 rows run
 // on the tensor-core kernel.  ``small``: the other rows (all rows without ``tile``) run on the warp kernel, their keys
-// cut into ``splits`` parts (1: uncut) through ``partial`` (fp32 [rows, heads, splits, 2 + vdim]).
+// cut into ``splits`` parts (1: uncut) through ``partial`` (fp32 [rows, heads, splits, 2 + 32 x the value columns a lane]).
 extern "C" int pih_window_attention(int dtype, const void* q, void* out, const void* cache, const void* block_table,
                                     int table_width, const void* request_of_row, const void* positions, const void* cu_q,
                                     const void* q_start, int rows, int requests, int heads, int kv_heads, int dim, int vdim,

@@ -1063,12 +1063,14 @@ class CudaOps:
             if self.lib.pih_window_attention_tile_takes(key_dim, value_dim) and cache.shape[2] % 8 == 0:
                 tile, small = (1 if plan[0] > 0 else 0), (1 if plan[1] > 0 else 0)
             if small:
-                # a row reads at most its window and the kept keys: as many parts as bring the GPU's warps to work,
-                # and no more than leave a part 128 keys
+                # a row reads at most its window and the kept keys: as many parts as bring the GPU's warps to work
+                # (32 a multiprocessor: a warp waits on its loads most of the time), and no more than leave a part
+                # 64 keys
                 reach = plan[2] if window <= 0 else min(plan[2], window + keep_first + 32)
-                splits = max(1, min(32, (148 * 16) // max(1, rows * heads), max(1, reach // 128)))
+                splits = max(1, min(32, (148 * 32) // max(1, rows * heads), max(1, reach // 64)))
                 if splits > 1:
-                    partial = torch.empty(rows * heads * splits * (2 + value_dim), dtype=torch.float32, device=q.device)
+                    per_lane = 2 if value_dim <= 64 else (4 if value_dim <= 128 else (8 if value_dim <= 256 else 16))
+                    partial = torch.empty(rows * heads * splits * (2 + 32 * per_lane), dtype=torch.float32, device=q.device)
         distances = bias.shape[1] if bias is not None else 0
         rc = self.lib.pih_window_attention(
             _DT[q.dtype], _ptr(q), _ptr(out), _ptr(cache), _ptr(block_table), block_table.shape[1],
