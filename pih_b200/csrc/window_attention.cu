@@ -448,15 +448,18 @@ window_attention_merge_kernel(const float* __restrict__ partial, T* __restrict__
                        out + unit * vdim, error);
 }
 
-// Tensor cores for requests of more than small_rows rows (bf16).  A block is 64 consecutive rows of one request and one
+// Tensor cores for requests of more than small_rows rows (bf16).  A block is kTileRows consecutive rows of one request and one
 // head (found on the device from cu_q: block x of the grid is the x-th such tile of the step, blocks beyond the last
 // leave); a warp is 16 of the rows.  Key tiles of 64 (the keys and values of the head's key/value head) come by
 // cp.async into two buffers: first the tiles that hold kept first tokens before the window, then the window's; columns
 // beyond dim / vdim up to the instance's DIM / VDIM are zeros.  Per warp: S = Q K^T (32-bit), the score finished (scale,
 // cap, bias by distance), the running maximum and sum of a row in the exp2 domain, P as a bf16 pair (rounding,
 // remainder) into O += P V.  At the end the sink joins the sum and the gate multiplies.
+constexpr int kTileWarps = 8;                               // 16 rows a warp: 128 rows a block, two blocks a multiprocessor
+constexpr int kTileRows = 16 * kTileWarps, kTileThreads = 32 * kTileWarps;
+
 template <int DIM, int VDIM>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kTileThreads, 2)
 window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out,
                              const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table, int table_width,
                              const int* __restrict__ cu_q, const int* __restrict__ q_start, int requests, int heads,
@@ -468,11 +471,11 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
   constexpr int QC = DIM / 8, VC = VDIM / 8, PER = QC + VC;   // 16-byte pieces of a row of q or k, of v, of a key
   constexpr float kLog2e = 1.4426950408889634f;
   extern __shared__ __align__(16) unsigned char window_tile_smem[];
-  bf16* Qs = reinterpret_cast<bf16*>(window_tile_smem);       // [64][QLD]
-  bf16* Ks = Qs + 64 * QLD;                                   // [2][64][QLD]
+  bf16* Qs = reinterpret_cast<bf16*>(window_tile_smem);       // [kTileRows][QLD]
+  bf16* Ks = Qs + kTileRows * QLD;                                   // [2][64][QLD]
   bf16* Vs = Ks + 2 * 64 * QLD;                               // [2][64][VLD]
   __shared__ int tile_info[2];
-  __shared__ float bias_s[2][128];                            // the bias of a key tile by (row - key) + 63 of the block
+  __shared__ float bias_s[2][kTileRows + 64];                 // the bias of a key tile by (row - key) + 63 of the block
   wait_for_prior_kernels();
   launch_dependents();
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -482,8 +485,8 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
     for (int r = 0; r < requests; ++r) {
       const int n = cu_q[r + 1] - cu_q[r];
       if (n <= small_rows) continue;
-      const int tiles = (n + 63) >> 6;
-      if (t < tiles) { found = r; at = cu_q[r] + t * 64; break; }
+      const int tiles = (n + kTileRows - 1) / kTileRows;
+      if (t < tiles) { found = r; at = cu_q[r] + t * kTileRows; break; }
       t -= tiles;
     }
     tile_info[0] = found;
@@ -493,7 +496,7 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
   const int req = tile_info[0];
   if (req < 0) return;
   const int row0 = tile_info[1];
-  const int nrows = min(64, cu_q[req + 1] - row0);
+  const int nrows = min(kTileRows, cu_q[req + 1] - row0);
   const int pos0 = q_start[req] + (row0 - cu_q[req]);
   const int head = blockIdx.y, g = head / (heads / kv_heads);
   const long long width = static_cast<long long>(kv_heads) * (dim + vdim);
@@ -505,15 +508,16 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
   const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
   const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
-  for (int c = tid; c < 64 * QC; c += 128) {
+  for (int c = tid; c < kTileRows * QC; c += kTileThreads) {
     const int rr = c / QC, col = (c % QC) * 8;
     bf16* dst = Qs + rr * QLD + col;
     if (rr < nrows && col < dim) mma::copy_async_16(dst, q + (static_cast<long long>(row0 + rr) * heads + head) * dim + col);
     else *reinterpret_cast<uint4*>(dst) = zero;
   }
-  // two threads a key: the key's place in the cache is looked up once, its pieces are dealt round
+  // kTileThreads / 64 threads a key: each looks the key's place in the cache up, the pieces are dealt round
+  constexpr int kPerKey = kTileThreads / 64;
   auto load_keys = [&](int buf, int j0) {
-    const int key = tid >> 1, j = j0 + key;
+    const int key = tid / kPerKey, j = j0 + key;
     bf16* kb = Ks + (buf * 64 + key) * QLD;
     bf16* vb = Vs + (buf * 64 + key) * VLD;
     long long at = -1;
@@ -526,7 +530,7 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
     const bf16* ksrc = cache + at + static_cast<long long>(g) * dim;
     const bf16* vsrc = cache + at + static_cast<long long>(kv_heads) * dim + static_cast<long long>(g) * vdim;
 #pragma unroll
-    for (int cc = (tid & 1); cc < PER; cc += 2) {
+    for (int cc = tid % kPerKey; cc < PER; cc += kPerKey) {
       if (cc < QC) {
         const int col = cc * 8;
         if (at >= 0 && col < dim) mma::copy_async_16(kb + col, ksrc + col);
@@ -537,7 +541,7 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
         else *reinterpret_cast<uint4*>(vb + col) = zero;
       }
     }
-    if (bias_of_head != nullptr && tid < 127)                 // distance (pos0 + row) - (j0 + key), row - key = tid - 63
+    if (bias_of_head != nullptr && tid < kTileRows + 63)      // distance (pos0 + row) - (j0 + key), row - key = tid - 63
       mma::copy_async_4(&bias_s[buf][tid], bias_of_head + min(max(pos0 - j0 + tid - 63, 0), rule.distances - 1));
     mma::copy_async_commit();
   };
@@ -661,12 +665,14 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
       }
       l_a = fmaf(l_a, fix_a, sum_a);
       l_b = fmaf(l_b, fix_b, sum_b);
+      if (__any_sync(0xffffffffu, fix_a != 1.0f || fix_b != 1.0f)) {   // (a maximum that stays leaves the sums as they are)
 #pragma unroll
-      for (int n = 0; n < VDIM / 8; ++n) {
-        O[n][0] *= fix_a;
-        O[n][1] *= fix_a;
-        O[n][2] *= fix_b;
-        O[n][3] *= fix_b;
+        for (int n = 0; n < VDIM / 8; ++n) {
+          O[n][0] *= fix_a;
+          O[n][1] *= fix_a;
+          O[n][2] *= fix_b;
+          O[n][3] *= fix_b;
+        }
       }
       {
         // 16 keys by 64 value columns a step: the values of the next step are asked for before this step's products;
@@ -709,7 +715,8 @@ window_attention_tile_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16*
         }
       }
     }
-    __syncthreads();
+    // (no barrier here: the next copies into this tile's buffers are issued behind the next step's barrier, which no
+    // warp passes before every warp has left this step)
   }
   if (wr0 >= nrows) return;
   l_a += __shfl_xor_sync(0xffffffffu, l_a, 1);
@@ -783,14 +790,14 @@ static int launch_window_tile(cudaStream_t s, unsigned tiles, const void* q, voi
                               const void* block_table, int table_width, const void* cu_q, const void* q_start, int requests,
                               int heads, int kv_heads, int dim, int vdim, int page_size, int num_pages, const WindowRule& rule,
                               const void* sink, const void* gate, long long ld_gate, int small_rows, void* error) {
-  const size_t smem = (static_cast<size_t>(3) * 64 * (DIM + 8) + 2 * 64 * (VDIM + 8)) * sizeof(bf16);
+  const size_t smem = ((static_cast<size_t>(kTileRows) + 2 * 64) * (DIM + 8) + 2 * 64 * (VDIM + 8)) * sizeof(bf16);
   static bool raised = false;
   if (!raised && smem > 48 * 1024) {
     cudaFuncSetAttribute(window_attention_tile_kernel<DIM, VDIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                          static_cast<int>(smem));
     raised = true;
   }
-  launch_kernel(window_attention_tile_kernel<DIM, VDIM>, dim3(tiles, heads), dim3(128), smem, s, static_cast<const bf16*>(q),
+  launch_kernel(window_attention_tile_kernel<DIM, VDIM>, dim3(tiles, heads), dim3(kTileThreads), smem, s, static_cast<const bf16*>(q),
                 static_cast<bf16*>(out), static_cast<const bf16*>(cache), static_cast<const int*>(block_table), table_width,
                 static_cast<const int*>(cu_q), static_cast<const int*>(q_start), requests, heads, kv_heads, dim, vdim,
                 page_size, num_pages, rule, static_cast<const float*>(sink), static_cast<const bf16*>(gate), ld_gate,
@@ -830,7 +837,7 @@ extern "C" int pih_window_attention(int dtype, const void* q, void* out, const v
   rule.distances = distances;
   const int small_rows = tile ? 16 : 0x7fffffff;
   if (tile) {
-    const unsigned tiles = static_cast<unsigned>((rows + 63) / 64 + requests);
+    const unsigned tiles = static_cast<unsigned>((rows + kTileRows - 1) / kTileRows + requests);
     int rc;
 #define PIH_TILE(D, V)                                                                                                 \
   rc = launch_window_tile<D, V>(s, tiles, q, out, cache, block_table, table_width, cu_q, q_start, requests, heads,    \
