@@ -126,13 +126,16 @@ constexpr int kMaxStreams = 8;
 //   x_t <- sum_s mix[s][t] x_s + spread[t] y        for all t at once, from the old streams
 // (stored back unless ``gather`` selects rows: then the row is only read).  With ``collect``:
 //   u = sum_t collect[t] x_t;   out = u / sqrt(mean(u^2) + eps) * weight                (weight null: out = u)
-// rounded to TO.  All sums 32-bit, in the order of the streams.
-template <typename TY, typename TO>
+// rounded to TO.  All sums 32-bit, in the order of the streams.  SC: the number of streams where the instance knows it
+// (0: any number up to kMaxStreams); V: columns a thread takes at a time (4: 16-byte loads of the streams).
+template <typename TY, typename TO, int SC, int V>
 __global__ void __launch_bounds__(256)
 hyper_stream_kernel(float* __restrict__ x, const TY* __restrict__ y, long long ldy, const float* __restrict__ mix,
                     const float* __restrict__ spread, const float* __restrict__ collect, const float* __restrict__ weight,
-                    const int* __restrict__ gather, TO* __restrict__ out, int S, int width, float eps) {
-  extern __shared__ float hyper_u[];                           // [width]
+                    const int* __restrict__ gather, TO* __restrict__ out, int streams, int width, float eps) {
+  constexpr int NS = SC > 0 ? SC : kMaxStreams;
+  const int S = SC > 0 ? SC : streams;
+  extern __shared__ __align__(16) float hyper_u[];             // [width]
   __shared__ float scratch[33];
   __shared__ float coef[kMaxStreams * kMaxStreams + 2 * kMaxStreams];
   wait_for_prior_kernels();
@@ -150,37 +153,71 @@ hyper_stream_kernel(float* __restrict__ x, const TY* __restrict__ y, long long l
   float* xr = x + row * S * width;
   const TY* yr = y != nullptr ? y + row * ldy : nullptr;
   float ss = 0.0f;
-  for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    float v[kMaxStreams];
+  for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {
+    float v[NS][V];
 #pragma unroll
-    for (int s = 0; s < kMaxStreams; ++s) v[s] = s < S ? xr[static_cast<long long>(s) * width + c] : 0.0f;
-    if (yr != nullptr) {
-      const float yv = to_float<TY>(yr[c]);
-      float n[kMaxStreams];
-#pragma unroll
-      for (int t = 0; t < kMaxStreams; ++t) {
-        float acc = 0.0f;
-        if (t < S) {
-#pragma unroll
-          for (int s = 0; s < kMaxStreams; ++s)
-            if (s < S) acc = fmaf(m[s * S + t], v[s], acc);
-          acc = fmaf(sp[t], yv, acc);
+    for (int s = 0; s < NS; ++s) {
+      if (s < S) {
+        if constexpr (V == 4) {
+          const float4 r = *reinterpret_cast<const float4*>(xr + static_cast<long long>(s) * width + c);
+          v[s][0] = r.x; v[s][1] = r.y; v[s][2] = r.z; v[s][3] = r.w;
+        } else {
+          v[s][0] = xr[static_cast<long long>(s) * width + c];
         }
-        n[t] = acc;
+      } else {
+#pragma unroll
+        for (int i = 0; i < V; ++i) v[s][i] = 0.0f;
+      }
+    }
+    if (yr != nullptr) {
+      float yv[V];
+      if constexpr (V == 4 && sizeof(TY) == 2) {
+        const uint2 r = *reinterpret_cast<const uint2*>(yr + c);
+        yv[0] = __uint_as_float(r.x << 16); yv[1] = __uint_as_float(r.x & 0xffff0000u);
+        yv[2] = __uint_as_float(r.y << 16); yv[3] = __uint_as_float(r.y & 0xffff0000u);
+      } else if constexpr (V == 4) {
+        const float4 r = *reinterpret_cast<const float4*>(yr + c);
+        yv[0] = r.x; yv[1] = r.y; yv[2] = r.z; yv[3] = r.w;
+      } else {
+        yv[0] = to_float<TY>(yr[c]);
+      }
+      float n[NS][V];
+#pragma unroll
+      for (int t = 0; t < NS; ++t) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float acc = 0.0f;
+          if (t < S) {
+#pragma unroll
+            for (int s = 0; s < NS; ++s)
+              if (s < S) acc = fmaf(m[s * S + t], v[s][i], acc);
+            acc = fmaf(sp[t], yv[i], acc);
+          }
+          n[t][i] = acc;
+        }
       }
 #pragma unroll
-      for (int t = 0; t < kMaxStreams; ++t) {
-        v[t] = n[t];
-        if (t < S && gather == nullptr) xr[static_cast<long long>(t) * width + c] = n[t];
+      for (int t = 0; t < NS; ++t) {
+#pragma unroll
+        for (int i = 0; i < V; ++i) v[t][i] = n[t][i];
+        if (t < S && gather == nullptr) {
+          if constexpr (V == 4)
+            *reinterpret_cast<float4*>(xr + static_cast<long long>(t) * width + c) = make_float4(n[t][0], n[t][1], n[t][2], n[t][3]);
+          else
+            xr[static_cast<long long>(t) * width + c] = n[t][0];
+        }
       }
     }
     if (collect != nullptr) {
-      float u = 0.0f;
 #pragma unroll
-      for (int t = 0; t < kMaxStreams; ++t)
-        if (t < S) u = fmaf(co[t], v[t], u);
-      hyper_u[c] = u;
-      ss = fmaf(u, u, ss);
+      for (int i = 0; i < V; ++i) {
+        float u = 0.0f;
+#pragma unroll
+        for (int t = 0; t < NS; ++t)
+          if (t < S) u = fmaf(co[t], v[t][i], u);
+        hyper_u[c + i] = u;
+        ss = fmaf(u, u, ss);
+      }
     }
   }
   if (collect == nullptr) return;
@@ -190,8 +227,11 @@ hyper_stream_kernel(float* __restrict__ x, const TY* __restrict__ y, long long l
     inv = 1.0f / sqrtf(ss / static_cast<float>(width) + eps);
   }
   TO* o = out + static_cast<long long>(blockIdx.x) * width;
-  for (int c = threadIdx.x; c < width; c += blockDim.x)          // (a thread reads back what it wrote itself)
-    o[c] = from_float<TO>(weight != nullptr ? hyper_u[c] * inv * weight[c] : hyper_u[c]);
+  for (int c = threadIdx.x * V; c < width; c += blockDim.x * V) {  // (a thread reads back what it wrote itself)
+#pragma unroll
+    for (int i = 0; i < V; ++i)
+      o[c + i] = from_float<TO>(weight != nullptr ? hyper_u[c + i] * inv * weight[c + i] : hyper_u[c + i]);
+  }
 }
 
 }  // namespace pih
@@ -314,24 +354,34 @@ extern "C" int pih_hyper_stream(int y_dtype, int out_dtype, void* x, const void*
   if (static_cast<size_t>(width) * sizeof(float) > 96 * 1024) return PIH_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const size_t smem = collect != nullptr ? static_cast<size_t>(width) * sizeof(float) : 0;
-  const dim3 grid(out_rows), block(width >= 1024 ? 256 : 128);
-#define PIH_HS(TY, TO)                                                                                                 \
+  const dim3 grid(out_rows), block(width >= 2048 ? 256 : 128);
+  const bool wide = width % 4 == 0 && ldy % 4 == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 &&
+                    reinterpret_cast<uintptr_t>(y) % 16 == 0;
+#define PIH_HS_I(TY, TO, SC, V)                                                                                        \
   do {                                                                                                                 \
     static bool raised = false;                                                                                        \
     if (!raised && smem > 48 * 1024) {                                                                                 \
-      cudaFuncSetAttribute(hyper_stream_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024);       \
+      cudaFuncSetAttribute(hyper_stream_kernel<TY, TO, SC, V>, cudaFuncAttributeMaxDynamicSharedMemorySize, 96 * 1024); \
       raised = true;                                                                                                   \
     }                                                                                                                  \
-    launch_kernel(hyper_stream_kernel<TY, TO>, grid, block, smem, s, static_cast<float*>(x), static_cast<const TY*>(y), \
-                  ldy, static_cast<const float*>(mix), static_cast<const float*>(spread),                              \
+    launch_kernel(hyper_stream_kernel<TY, TO, SC, V>, grid, block, smem, s, static_cast<float*>(x),                    \
+                  static_cast<const TY*>(y), ldy, static_cast<const float*>(mix), static_cast<const float*>(spread),   \
                   static_cast<const float*>(collect), static_cast<const float*>(weight), static_cast<const int*>(gather), \
                   static_cast<TO*>(out), streams, width, eps);                                                         \
+  } while (0)
+#define PIH_HS(TY, TO)                                                                                                 \
+  do {                                                                                                                 \
+    if (wide && streams == 2) PIH_HS_I(TY, TO, 2, 4);                                                                  \
+    else if (wide && streams == 4) PIH_HS_I(TY, TO, 4, 4);                                                             \
+    else if (wide) PIH_HS_I(TY, TO, 0, 4);                                                                             \
+    else PIH_HS_I(TY, TO, 0, 1);                                                                                       \
   } while (0)
   if (y_dtype == PIH_BF16 && out_dtype == PIH_BF16) PIH_HS(bf16, bf16);
   else if (y_dtype == PIH_F32 && out_dtype == PIH_F32) PIH_HS(float, float);
   else if (y_dtype == PIH_BF16 && out_dtype == PIH_F32) PIH_HS(bf16, float);
   else if (y_dtype == PIH_F32 && out_dtype == PIH_BF16) PIH_HS(float, bf16);
   else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_HS_I
 #undef PIH_HS
   PIH_LAUNCH_CHECK();
   return 0;
