@@ -86,6 +86,7 @@ struct SkinnyParams {
   int M, N, K;
   long long ldx, ldw, ldo;
   int stages;                                    // of the ring of units
+  int activation;                                // of the gated epilogue: 0 SiLU, 1 the tanh form of GELU
   uint32_t* error;
 };
 
@@ -328,7 +329,10 @@ __global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const Skinny
       if (col < N / 2) {
         g = __bfloat162float(__float2bfloat16_rn(g));
         u = __bfloat162float(__float2bfloat16_rn(u));
-        out[etok * p.ldo + col] = from_float<OT>((g / (1.0f + expf(-g))) * u);
+        // GELU: z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), 1 + tanh(a) written as 2 - 2 / (e^{2a} + 1)
+        const float a = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
+        const float act = p.activation == 1 ? g * (1.0f - __fdividef(1.0f, __expf(2.0f * a) + 1.0f)) : g / (1.0f + expf(-g));
+        out[etok * p.ldo + col] = from_float<OT>(act * u);
       }
     } else {
 #pragma unroll
@@ -589,7 +593,8 @@ extern "C" int pih_set_skinny_rule(int on) {
 //   delta      nullable: the rows are round(x + delta), as the fused add of a pre-norm block; the sums are also
 //              written to x_out (a buffer other than x: blocks read x while one of them writes)
 //   norm_w     nullable: RMSNorm (weight dtype norm_dtype, eps) of the rows before the product
-//   swiglu     W rows come in blocks of 16 = 8 gate rows + their 8 up rows; out is [M, N / 2]
+//   swiglu     W rows come in blocks of 16 = 8 gate rows + their 8 up rows; out is [M, N / 2]; 1: SiLU(gate) * up,
+//              2: the tanh form of GELU instead of SiLU
 //   residual   nullable (not with swiglu): out = round(round(x . W^T) + residual), the residual add that follows an
 //              output projection, with its two roundings; rows of ldo elements; may not be `out` itself
 //   error      the device's error word (a bounded wait that ran out is reported there)
@@ -628,6 +633,7 @@ extern "C" int pih_gemm_skinny(const void* x, const void* delta, void* x_out, in
   p.ldx = ldx, p.ldw = ldw, p.ldo = ldo;
   p.error = error;
   const bool sw = swiglu != 0;
+  p.activation = swiglu == 2 ? 1 : 0;
 #define PIH_SKINNY(MR, NORM, NW) dispatch_skinny<MR, NORM, NW>(sw, p, s)
   if (norm_w == nullptr) return M <= 8 ? PIH_SKINNY(8, false, float) : PIH_SKINNY(16, false, float);
   if (norm_dtype == PIH_F32) return M <= 8 ? PIH_SKINNY(8, true, float) : PIH_SKINNY(16, true, float);

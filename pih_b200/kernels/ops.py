@@ -253,9 +253,9 @@ class CudaOps:
         return torch.mm(x, w.t())
 
     def linear_skinny(self, x: torch.Tensor, w: torch.Tensor, *, delta=None, norm_weight=None, eps: float = 0.0,
-                      swiglu: bool = False, residual: Optional[torch.Tensor] = None):
+                      swiglu: bool = False, residual: Optional[torch.Tensor] = None, activation: str = "silu"):
         """The few-rows product (bf16, at most 16 rows) with its optional fused residual add, RMSNorm and
-        SwiGLU in front and behind.  ``residual``: the result is ``round(round(x . w^T) + residual)``.  Returns
+        SwiGLU (``activation`` "gelu_tanh": GELU in SiLU's place) in front and behind.  ``residual``: the result is ``round(round(x . w^T) + residual)``.  Returns
         ``out`` — or ``(x + delta, out)`` when ``delta`` is given — or None when the kernel does not take the shape."""
         M, K = x.shape
         N = w.shape[0]
@@ -268,7 +268,8 @@ class CudaOps:
         nd = _DT[norm_weight.dtype] if norm_weight is not None else 0
         rc = self.lib.pih_gemm_skinny(_ptr(x), _ptr(delta), _ptr(x_out), nd, _ptr(norm_weight), c_float(eps), _ptr(w),
                                       _ptr(out), _ptr(residual), M, N, K, c_ll(x.stride(0)), c_ll(w.stride(0)),
-                                      c_ll(out.stride(0)), 1 if swiglu else 0, self._err(), self._stream())
+                                      c_ll(out.stride(0)), (2 if activation == "gelu_tanh" else 1) if swiglu else 0,
+                                      self._err(), self._stream())
         if rc == -2:
             return None
         self._check(rc, "gemm_skinny")

@@ -9,8 +9,8 @@ gate rows and their 8 up rows) so that one product reads the activations
 once and can apply SiLU-mul in its epilogue.
 
 ``activation`` "gelu_tanh" makes it ``down( gelu(gate(x)) * up(x) )`` with the tanh form of GELU,
-``z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``: the same stacked product, the activation by its own kernel
-(the products' fused epilogues are SiLU's).
+``z / 2 (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3)))``: the same stacked product; the few-rows product applies it in
+its epilogue as it does SiLU, many rows get the activation's own kernel (the tcgen05 pair product's epilogue is SiLU's).
 """
 from __future__ import annotations
 
@@ -48,14 +48,14 @@ class SwiGLU:
 
     def forward(self, x):
         ops = self.rt.ops
-        if self.spec.activation != "silu":
-            return ops.linear(ops.act_mul(ops.linear(x, self.w_gate_up), self.interleave, self.spec.activation), self.w_down)
         act = None
         if self.interleave == 8 and x.shape[0] <= getattr(ops, "skinny_max_rows", 0) and hasattr(ops, "linear_skinny"):
-            act = ops.linear_skinny(x, self.w_gate_up, swiglu=True)      # few rows: SiLU-mul in the product's epilogue
+            # few rows: the activation and the multiplication in the product's epilogue
+            act = ops.linear_skinny(x, self.w_gate_up, swiglu=True, activation=self.spec.activation)
         if act is None:
             gate_up = ops.linear(x, self.w_gate_up)
-            act = ops.silu_mul(gate_up, self.interleave)
+            act = (ops.silu_mul(gate_up, self.interleave) if self.spec.activation == "silu"
+                   else ops.act_mul(gate_up, self.interleave, self.spec.activation))
         return ops.linear(act, self.w_down)
 
     def forward_prenorm(self, h, delta, norm):

@@ -283,3 +283,25 @@ def test_greedy_generation_through_the_engine(dirs, dtype):
             best = int(torch.argmax(row))
             gap = float(row[best] - row[tok])
             assert tok == best or gap < (1e-4 if dtype == "float32" else 0.03) * float(row.std()), (dtype, i, tok, best, gap)
+
+
+@pytest.mark.parametrize("rows", [1, 8, 13])
+def test_the_few_rows_product_with_gelu_in_its_epilogue(rows):
+    """``gelu(x Wg^T) * (x Wu^T)`` from the few-rows product (gate and up rows interleaved in blocks of 8) against the
+    formula on the bf16 roundings of the two products."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(rows)
+    hidden, ff = 96, 72
+    x = torch.randn(rows, hidden, generator=g).to(torch.bfloat16).to(DEV)
+    gate, up = (torch.randn(ff, hidden, generator=g).mul(0.3).to(torch.bfloat16) for _ in range(2))
+    stacked = torch.stack([gate.reshape(-1, 8, hidden), up.reshape(-1, 8, hidden)], dim=1).reshape(2 * ff, hidden).to(DEV)
+    got = ops.linear_skinny(x, stacked.contiguous(), swiglu=True, activation="gelu_tanh")
+    ops.check_errors()
+    assert got is not None and got.shape == (rows, ff)
+    a = (x.double().cpu() @ gate.double().t()).to(torch.bfloat16).double()
+    b = (x.double().cpu() @ up.double().t()).to(torch.bfloat16).double()
+    want = 0.5 * a * (1 + torch.tanh(math.sqrt(2 / math.pi) * (a + 0.044715 * a ** 3))) * b
+    # the products' roundings may fall on either side of a tie: a bf16 step of the inputs, and the output's own rounding
+    assert float((got.double().cpu() - want).abs().max()) < 0.02 * float(want.abs().max())
+    silu = ops.linear_skinny(x, stacked.contiguous(), swiglu=True)
+    assert float((silu.double().cpu() - a / (1 + torch.exp(-a)) * b).abs().max()) < 0.02 * float(want.abs().max())
