@@ -17,8 +17,8 @@
 //                            depend on the step's make-up by a single bit.  With splits the keys of a (row, head) of a
 //                            request of at most 16 rows are cut into parts side by side, folded in order by
 //                            window_attention_merge
-//   window_attention_tile    bf16, tensor cores (mma.sync m16n8k16), requests of more than 16 rows: a block is 64 rows of
-//                            a (request, head), a warp 16 of them; tiles of 64 keys by cp.async into two buffers, the
+//   window_attention_tile    bf16, tensor cores (mma.sync m16n8k16), requests of more than 16 rows: a block is 128 rows
+//                            of a (request, head), a warp 16 of them; tiles of 64 keys by cp.async into two buffers, the
 //                            tiles of the kept first tokens before those of the window; scores, softmax and sums
 //                            32-bit; the weights enter the product with the values as a bf16 pair (rounding and remainder)
 #include "common.cuh"
