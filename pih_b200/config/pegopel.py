@@ -111,7 +111,7 @@ class PegopelConfig:
         if not isinstance(m, dict):
             raise ValueError(f"config.json: {where} must be an object")
         heads, kv_heads, dim = _int(m, "heads", where), _int(m, "kv_heads", where), _int(m, "dim", where)
-        vdim = _int(m, "vdim", where)
+        vdim = _int(m, "vdim", where) if m.get("vdim") is not None else dim     # (not given: as wide as the keys)
         if heads % kv_heads:
             raise ValueError(f"config.json: {where}.heads must be a multiple of kv_heads")
         mask = _object(m, "mask", where)
@@ -119,7 +119,8 @@ class PegopelConfig:
                       scale=_number(m, "scale", where), window=_int(mask, "size", where + ".mask"),
                       norm_eps=self.norm_eps)
         if kind == "attention":
-            return WindowAttentionSpec(conv_taps=_int(m, "conv", where), bias_rows=self._bias_rows(i),
+            return WindowAttentionSpec(conv_taps=_int(m, "conv", where) if m.get("conv") is not None else 0,
+                                       bias_rows=self._bias_rows(i),
                                        bias_far=_number(m, "bias_max", where), sink="learned", **common)
         if vdim != dim:
             raise ValueError(f"config.json: {where}.vdim must equal dim: the values are the keys as projected")
