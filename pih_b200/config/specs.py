@@ -27,6 +27,7 @@ class NormSpec:
     eps: float
     kind: str = "rmsnorm"
     weight_name: str = "weight"       # behind the norm's prefix ("": the prefix itself names the tensor)
+    offset: float = 0.0               # the weight that multiplies is ``offset`` + the stored one (1.0: stored around zero)
 
 
 @dataclass(frozen=True)
@@ -128,8 +129,16 @@ class RGLRUSpec:
 @dataclass(frozen=True)
 class LatentAttentionSpec:
     """Causal attention whose keys and values are up-projections of one cached latent vector per token
-    (``latent_rank`` numbers, RMS-normed), without positions; the softmax denominator may hold a learned
-    per-head sink, and a per-head sigmoid gate may multiply the head's output."""
+    (``latent_rank`` numbers, RMS-normed); the softmax denominator may hold a learned per-head sink, and a sigmoid
+    gate may multiply the output: one number a head (``gate_per`` "head") or one a column of the concatenated heads
+    ("column").  Options, each a mechanism of its own:
+
+    * ``rotary_dim`` > 0 with ``position``: beside the ``key_dim`` numbers that come from the latent, every head's
+      query has ``rotary_dim`` rotated numbers (a head's query is laid out ``[key_dim | rotary_dim]``), and the down
+      projection has ``rotary_dim`` more rows: one rotated key part a token, not normed, shared by all heads and
+      cached behind the latent; the score is the sum of both dot products;
+    * ``query_rank``: the queries come through a latent of their own, ``q = W_uq rmsnorm(W_dq x)``;
+    * ``window``: a row sees the last ``window`` keys, its own included."""
     hidden: int
     heads: int
     key_dim: int
@@ -139,9 +148,23 @@ class LatentAttentionSpec:
     norm_eps: float
     sink: bool = True
     gated: bool = True
+    gate_per: str = "head"
+    rotary_dim: int = 0
+    position: Optional[object] = None
+    query_rank: Optional[int] = None
+    window: Optional[int] = None
     kind: str = "latent_attention"
     names: Mapping[str, str] = _names(q="mix.q", down="mix.dkv", down_norm="mix.dkv.norm", up_k="mix.uk",
-                                      up_v="mix.uv", sink="mix.sink", gate="mix.g", o="mix.o")
+                                      up_v="mix.uv", sink="mix.sink", gate="mix.g", o="mix.o", q_down="mix.dq",
+                                      q_down_norm="mix.dq.norm", q_up="mix.uq")
+
+    @property
+    def query_dim(self) -> int:
+        return self.key_dim + self.rotary_dim
+
+    @property
+    def cached_width(self) -> int:
+        return self.latent_rank + self.rotary_dim
 
 
 @dataclass(frozen=True)
@@ -159,11 +182,17 @@ class MoESpec:
 
 @dataclass(frozen=True)
 class ComputedRopeSpec:
-    """Rotate-half rotary encoding whose angles the kernels compute from the position (32-bit ``position * f_i`` with
-    ``f_i = theta^(-2i/rotary_dim)``): no table, so no longest context has to be known."""
+    """Rotary encoding whose angles the kernels compute from the position (32-bit ``position * f_i`` with
+    ``f_i = theta^(-2i/rotary_dim)``): no table, so no longest context has to be known.  The pairs are the halves
+    ``(i, i + rotary_dim / 2)`` or, with ``interleaved``, the neighbours ``(2i, 2i + 1)``.  ``stretch`` = (factor, low,
+    high, original) slows the slow pairs down: with ``turns_i = original f_i / (2 pi)`` (how often pair i goes round
+    within ``original`` positions) and ``t_i = clamp((turns_i - low) / (high - low), 0, 1)``, the frequency becomes
+    ``f_i (t_i + (1 - t_i) / factor)`` — untouched from ``high`` turns on, divided by ``factor`` up to ``low`` turns."""
     head_dim: int
     rotary_dim: int
     theta: float
+    interleaved: bool = False
+    stretch: Optional[Sequence[float]] = None
     kind: str = "rope_computed"
 
 
@@ -246,13 +275,30 @@ class BiasedMLPSpec:
 
 
 @dataclass(frozen=True)
+class PlainMLPSpec:
+    """Two-matrix feed-forward without biases or gate: ``W_down act(W_up x)``; ``activation`` "relu2": the square of
+    ``max(z, 0)``."""
+    hidden: int
+    intermediate: int
+    activation: str = "relu2"
+    kind: str = "plain_mlp"
+    names: Mapping[str, str] = _names(up="mlp.up", down="mlp.down")
+
+
+@dataclass(frozen=True)
 class ScoredMoESpec:
     """Mixture of gated feed-forward experts whose router scores every output with a softmax over ALL of them:
     ``experts`` real experts and behind them ``identity`` experts without tensors whose output is the input itself.
     The choice goes by ``score + correction`` (a learned vector), restricted to the ``groups_keep`` best of
     ``groups`` equal groups of neighbouring outputs (a group's score: its largest choice score); the ``top`` chosen
     outputs weigh with their scores, as they are (``renormalize`` False) or divided by their sum.  ``shared``: a
-    gated feed-forward that runs for every row and is added, multiplied by ``sigmoid`` of a one-row projection."""
+    gated feed-forward that runs for every row and is added, multiplied by ``sigmoid`` of a one-row projection
+    (``shared_gate`` False: added as it is; its spec may be any feed-forward's).
+
+    ``scoring`` "sigmoid": every output's score is the sigmoid of its own logit.  ``correction`` False: there is no
+    correction tensor.  ``gated`` False: an expert is ``W_down act(W_up x)`` (no gate matrix; ``activation`` "relu2":
+    the square of ``max(z, 0)``).  ``weigh`` "input": the weight multiplies what the expert READS, not what it gives:
+    the output is the sum of ``expert(weight * x)``."""
     hidden: int
     experts: int
     identity: int
@@ -261,8 +307,13 @@ class ScoredMoESpec:
     groups: int = 1
     groups_keep: int = 1
     renormalize: bool = False
-    shared: Optional[SwiGLUSpec] = None
+    shared: Optional[object] = None
     activation: str = "silu"
+    scoring: str = "softmax"
+    correction: bool = True
+    gated: bool = True
+    weigh: str = "output"
+    shared_gate: bool = True
     kind: str = "scored_moe"
     names: Mapping[str, str] = _names(router="mlp.router", correction="mlp.correction", expert="mlp.e{}.", gate="gate",
                                       up="up", down="down", shared_gate="mlp.shared.sg")
@@ -327,6 +378,12 @@ class WindowAttentionSpec:
     softcap: Optional[float] = None
     sink: str = "learned"
     head_gate: bool = False
+    # False: the mixer has no key/value tensors (projections, their convolutions and norms) and reads another entry's
+    # cache, with queries, window, sink and everything else of its own
+    own_kv: bool = True
+    # how many keys back the cache has to reach (another entry that reads this cache may look further back than
+    # ``window``); None: ``window``
+    cache_window: Optional[int] = None
     kind: str = "window_attention"
     names: Mapping[str, str] = _names(q="mix.q", k="mix.k", v="mix.v", o="mix.o", q_norm="mix.q.norm", k_norm="mix.k.norm",
                                       q_conv="mix.q.conv", k_conv="mix.k.conv", v_conv="mix.v.conv", bias="mix.rel",
@@ -384,6 +441,17 @@ class ScheduleEntry:
 
 
 @dataclass(frozen=True)
+class BigramSpec:
+    """A second embedding by the pair (previous token, token): row ``(previous * mul_prev + token * mul_cur) mod
+    buckets`` of the table ``name`` ``[buckets + 1, hidden]`` is added to the token's embedding; a sequence's first
+    token takes the table's last row.  The previous token is per-request state."""
+    buckets: int
+    mul_prev: int
+    mul_cur: int
+    name: str = "bigram"
+
+
+@dataclass(frozen=True)
 class ModelSpec:
     vocab: int
     hidden: int
@@ -404,6 +472,9 @@ class ModelSpec:
     # > 0: the model keeps this many copies of the residual stream (blocks of the "hyper" arrangement); its output is
     # the final norm of their sum
     streams: int = 0
+    # the logits are the head's product times this number
+    logit_scale: float = 1.0
+    bigram: Optional[BigramSpec] = None
 
     def validate(self) -> None:
         for i, e in enumerate(self.schedule):

@@ -22,6 +22,7 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 latent_write_kernel(const T* __restrict__ raw, long long ld, const float* __restrict__ weight, float eps,
                     T* __restrict__ cache, const int* __restrict__ slot_mapping, int rows, int rank, long long cache_rows,
+                    int rot, int interleaved, const float* __restrict__ freq, const int* __restrict__ positions,
                     uint32_t* err) {
   wait_for_prior_kernels();
   launch_dependents();
@@ -39,8 +40,23 @@ latent_write_kernel(const T* __restrict__ raw, long long ld, const float* __rest
   for (int i = lane; i < rank; i += 32) { const float a = to_float<T>(src[i]); ss = fmaf(a, a, ss); }
   ss = warp_sum(ss);
   const float scale = 1.0f / sqrtf(ss / static_cast<float>(rank) + eps);
-  T* dst = cache + static_cast<long long>(slot) * rank;
+  T* dst = cache + static_cast<long long>(slot) * (rank + rot);
   for (int i = lane; i < rank; i += 32) dst[i] = from_float<T>(to_float<T>(src[i]) * scale * weight[i]);
+  if (rot > 0) {
+    // behind the latent: ``rot`` more numbers, not normed, rotated by the row's position (32-bit angles)
+    const float place = static_cast<float>(positions[row]);
+    const int half = rot >> 1;
+    for (int c = lane; c < rot; c += 32) {
+      int pair, other;
+      bool first;
+      if (interleaved) { pair = c >> 1; first = (c & 1) == 0; other = first ? c + 1 : c - 1; }
+      else { pair = c < half ? c : c - half; first = c < half; other = first ? c + half : c - half; }
+      float sn, cs;
+      sincosf(place * freq[pair], &sn, &cs);
+      const float a = to_float<T>(src[rank + c]), b = to_float<T>(src[rank + other]);
+      dst[rank + c] = from_float<T>(first ? a * cs - b * sn : a * cs + b * sn);
+    }
+  }
 }
 
 constexpr int kLatentPerLane = 16;          // rank <= 32 * 16
@@ -479,16 +495,20 @@ latent_merge_kernel(const float* __restrict__ partial, const T* __restrict__ gat
 using namespace pih;
 typedef __nv_bfloat16 bf16;
 
+// raw [rows, ld]: ``rank`` numbers that are normed and, behind them, ``rot`` numbers that are rotated by
+// positions[row] * freq[pair] (pairs of neighbours with ``interleaved``, else halves); cache [slots, rank + rot].
 extern "C" int pih_latent_write(int dtype, const void* raw, long long ld, const void* weight, float eps, void* cache,
-                                const void* slot_mapping, int rows, int rank, int page_size, int num_pages, void* err,
-                                void* stream) {
+                                const void* slot_mapping, int rows, int rank, int page_size, int num_pages, int rot,
+                                int interleaved, const void* freq, const void* positions, void* err, void* stream) {
   if (rows <= 0) return 0;
+  if (rot < 0 || (rot & 1) || (rot > 0 && (freq == nullptr || positions == nullptr))) return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long cache_rows = static_cast<long long>(page_size) * num_pages;
 #define PIH_LW(T)                                                                                                      \
   launch_kernel(latent_write_kernel<T>, dim3((rows + 3) / 4), dim3(128), 0, s, static_cast<const T*>(raw), ld,         \
                 static_cast<const float*>(weight), eps, static_cast<T*>(cache), static_cast<const int*>(slot_mapping), \
-                rows, rank, cache_rows, static_cast<uint32_t*>(err))
+                rows, rank, cache_rows, rot, interleaved, static_cast<const float*>(freq),                             \
+                static_cast<const int*>(positions), static_cast<uint32_t*>(err))
   if (dtype == PIH_F32) PIH_LW(float);
   else if (dtype == PIH_BF16) PIH_LW(bf16);
   else return PIH_ERR_BAD_ARGUMENT;

@@ -73,13 +73,14 @@ moe_route_kernel(const float* __restrict__ logits, int rows, int experts, int to
   }
 }
 
-// Routing by scores over ALL outputs: s = softmax(logits); the choice goes by s + correction, among the outputs of the
+// Routing by scores over ALL outputs: s = softmax(logits), or with ``scoring`` 1 the sigmoid of each logit by itself;
+// the choice goes by s + correction, among the outputs of the
 // ``keep`` best of ``groups`` equal groups of neighbours (a group's score: its largest choice score; the others count
 // as minus infinity); the ``top`` largest are chosen (ties: the smaller index) and weigh with their s, divided by the
 // chosen ones' sum only with ``renormalize``.  One warp a row; ``flags``: [warps][groups] ints of shared memory.
 __global__ void __launch_bounds__(128)
 moe_route_scored_kernel(const float* __restrict__ logits, long long ld, const float* __restrict__ correction, int rows,
-                        int experts, int top, int groups, int keep, int renormalize, int* __restrict__ expert_of,
+                        int experts, int top, int groups, int keep, int renormalize, int scoring, int* __restrict__ expert_of,
                         float* __restrict__ weight_of, int* __restrict__ rank_of, int* __restrict__ counts,
                         int* __restrict__ pos_of) {
   extern __shared__ float route_smem[];
@@ -103,11 +104,12 @@ moe_route_scored_kernel(const float* __restrict__ logits, long long ld, const fl
   float sum = 0.0f;
 #pragma unroll
   for (int e = 0; e < kPer; ++e) {
-    sc[e] = (e * 32 < experts && sc[e] != -INFINITY) ? expf(sc[e] - mx) : 0.0f;
+    if (scoring == 1) sc[e] = (e * 32 < experts && sc[e] != -INFINITY) ? 1.0f / (1.0f + expf(-sc[e])) : 0.0f;
+    else sc[e] = (e * 32 < experts && sc[e] != -INFINITY) ? expf(sc[e] - mx) : 0.0f;
     sum += sc[e];
   }
   sum = warp_sum(sum);
-  const float inv = 1.0f / sum;
+  const float inv = scoring == 1 ? 1.0f : 1.0f / sum;         // (a sigmoid score stands for itself)
 #pragma unroll
   for (int e = 0; e < kPer; ++e) {
     const int i = lane + 32 * e;
@@ -193,7 +195,7 @@ __global__ void moe_plan_kernel(const int* __restrict__ counts, int experts, int
 
 __global__ void moe_scatter_kernel(const int* __restrict__ expert_of, const int* __restrict__ rank_of,
                                    const int* __restrict__ plan, int slots, int top, int* __restrict__ pos_of,
-                                   int* __restrict__ row_of) {
+                                   int* __restrict__ row_of, int* __restrict__ slot_of) {
   wait_for_prior_kernels();
   launch_dependents();
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -201,22 +203,28 @@ __global__ void moe_scatter_kernel(const int* __restrict__ expert_of, const int*
   const int pos = plan[expert_of[i]] + rank_of[i];
   pos_of[i] = pos;
   row_of[pos] = i / top;
+  slot_of[pos] = i;
 }
 
-// The grouped product.  kGated: two weight matrices per expert and silu(a) * b in the epilogue.  A's rows are
-// gathered through ``row_of`` when it is given (else row = position).  Expert e's matrices [N, K] start
+// The grouped product.  kForm 1: two weight matrices per expert and silu(a) * b in the epilogue; 2: one matrix and the
+// square of max(a, 0); 0: one matrix, the product as it is.  A's rows are gathered through ``row_of`` when it is given
+// (else row = position); with ``in_weight`` a gathered row is multiplied by the weight of its slot (``slot_of`` by
+// position) and rounded to the storage type: the expert reads the weighted row.  Expert e's matrices [N, K] start
 // ``e * expert_stride`` elements behind W0 and W1.
-template <typename TA, typename TC, bool kGated>
+template <typename TA, typename TC, int kForm>
 __global__ void __launch_bounds__(256)
 moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restrict__ row_of, const TA* __restrict__ W0,
                    const TA* __restrict__ W1, long long expert_stride, TC* __restrict__ C, long long ldc,
-                   const int* __restrict__ plan, int experts, int with_matrices, int N, int K) {
+                   const int* __restrict__ plan, int experts, int with_matrices, int N, int K,
+                   const float* __restrict__ in_weight, const int* __restrict__ slot_of) {
+  constexpr bool kGated = kForm == 1;
   constexpr int BM = kMoeTile, BN = 64, BK = 16, TM = 4, TN = 4;
   wait_for_prior_kernels();
   launch_dependents();
   __shared__ float As[BK][BM + 4];
   __shared__ float Ws[kGated ? 2 : 1][BK][BN + 4];
   __shared__ int rows_s[BM];
+  __shared__ float weight_s[BM];
   __shared__ int info[3];
   const int tid = threadIdx.x;
   if (tid == 0) {
@@ -241,7 +249,10 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
   const int e = info[0];
   if (e < 0 || e >= with_matrices) return;                      // (an identity expert has no matrices: its rows are the combine's)
   const int p0 = info[1], m_rows = info[2];
-  if (tid < BM) rows_s[tid] = tid < m_rows ? (row_of != nullptr ? row_of[p0 + tid] : p0 + tid) : -1;
+  if (tid < BM) {
+    rows_s[tid] = tid < m_rows ? (row_of != nullptr ? row_of[p0 + tid] : p0 + tid) : -1;
+    weight_s[tid] = (tid < m_rows && in_weight != nullptr) ? in_weight[slot_of[p0 + tid]] : 1.0f;
+  }
   __syncthreads();
   const int tx = tid % (BN / TN), ty = tid / (BN / TN);
   const int n0 = blockIdx.x * BN;
@@ -261,7 +272,9 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
       const int r = el / BK, c = el % BK;
       const int gk = k0 + c, gn = n0 + r;
       const int src = rows_s[r];
-      As[c][r] = (src >= 0 && gk < K) ? to_float<TA>(A[static_cast<long long>(src) * lda + gk]) : 0.0f;
+      float a = (src >= 0 && gk < K) ? to_float<TA>(A[static_cast<long long>(src) * lda + gk]) : 0.0f;
+      if (in_weight != nullptr) a = round_to<TA>(a * weight_s[r]);
+      As[c][r] = a;
       Ws[0][c][r] = (gn < N && gk < K) ? to_float<TA>(w0[static_cast<long long>(gn) * K + gk]) : 0.0f;
       if (kGated) Ws[1][c][r] = (gn < N && gk < K) ? to_float<TA>(w1[static_cast<long long>(gn) * K + gk]) : 0.0f;
     }
@@ -310,6 +323,9 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
         // the two products are rounded to the storage type before the activation, as separate products would be
         const float a = round_to<TA>(acc[0][i][j]), b = round_to<TA>(acc[kGated ? 1 : 0][i][j]);
         val = (a / (1.0f + expf(-a))) * b;
+      } else if (kForm == 2) {
+        const float a = fmaxf(round_to<TA>(acc[0][i][j]), 0.0f);
+        val = a * a;
       } else {
         val = acc[0][i][j];
       }
@@ -320,13 +336,17 @@ moe_grouped_kernel(const TA* __restrict__ A, long long lda, const int* __restric
 
 
 // Few rows (a decode step): every (row, choice) slot on its own, a warp an output column, the expert's weight rows
-// read with 16-byte loads, four columns in flight a warp.  x row of slot s: s / row_div.  kGated: act[s][n] =
-// silu(x . W0_e[n]) * (x . W1_e[n]); else out[out_index[s]][n] = x . W0_e[n] (32-bit).  K a multiple of 8 (4 in 32-bit).
-template <typename T, typename TC, bool kGated>
+// read with 16-byte loads, four columns in flight a warp.  x row of slot s: s / row_div.  kForm 1: act[s][n] =
+// silu(x . W0_e[n]) * (x . W1_e[n]); 2: act[s][n] = max(x . W0_e[n], 0)^2; 0: out[out_index[s]][n] = x . W0_e[n]
+// (32-bit).  With ``in_weight`` the row is multiplied by the slot's weight and rounded to the storage type first.
+// K a multiple of 8 (4 in 32-bit).
+template <typename T, typename TC, int kForm>
 __global__ void __launch_bounds__(256)
 moe_gemv_kernel(const T* __restrict__ x, long long ldx, int row_div, const int* __restrict__ expert_of,
                 const T* __restrict__ W0, const T* __restrict__ W1, long long expert_stride, TC* __restrict__ out,
-                long long ldo, const int* __restrict__ out_index, int with_matrices, int N, int K) {
+                long long ldo, const int* __restrict__ out_index, int with_matrices, int N, int K,
+                const float* __restrict__ in_weight) {
+  constexpr bool kGated = kForm == 1;
   constexpr int kVec = 16 / sizeof(T), kCols = 4;
   extern __shared__ float xs[];
   wait_for_prior_kernels();
@@ -335,7 +355,9 @@ moe_gemv_kernel(const T* __restrict__ x, long long ldx, int row_div, const int* 
   const int e = expert_of[slot];
   if (e >= with_matrices) return;                               // an identity expert: the combine takes the row itself
   const T* xr = x + static_cast<long long>(slot / row_div) * ldx;
-  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float<T>(xr[k]);
+  const float scale_in = in_weight != nullptr ? in_weight[slot] : 1.0f;
+  for (int k = threadIdx.x; k < K; k += blockDim.x)
+    xs[k] = in_weight != nullptr ? round_to<T>(to_float<T>(xr[k]) * scale_in) : to_float<T>(xr[k]);
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n0 = (blockIdx.y * (blockDim.x >> 5) + warp) * kCols;
@@ -373,6 +395,9 @@ moe_gemv_kernel(const T* __restrict__ x, long long ldx, int row_div, const int* 
         g = round_to<T>(g);
         u = round_to<T>(u);
         out[orow * ldo + n0 + c] = from_float<TC>((g / (1.0f + expf(-g))) * u);
+      } else if (kForm == 2) {
+        g = fmaxf(round_to<T>(g), 0.0f);
+        out[orow * ldo + n0 + c] = from_float<TC>(g * g);
       } else {
         out[orow * ldo + n0 + c] = from_float<TC>(g);
       }
@@ -421,12 +446,13 @@ batched_gemv_kernel(const T* __restrict__ x, long long ldx, long long batch_x, c
   }
 }
 
-// An expert from ``with_matrices`` on is an identity expert: its output is the row of x itself.
+// An expert from ``with_matrices`` on is an identity expert: its output is the row of x itself.  ``unit_weights``: the
+// weights were applied to what the experts read; the outputs are summed as they are.
 template <typename T, typename TY>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ pos_of,
                                    const float* __restrict__ weight_of, T* __restrict__ out, int rows, int hidden, int top,
                                    const int* __restrict__ expert_of, int with_matrices, const T* __restrict__ x,
-                                   long long ldx) {
+                                   long long ldx, int unit_weights) {
   wait_for_prior_kernels();
   launch_dependents();
   const int row = blockIdx.x;
@@ -436,7 +462,7 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
       const long long i = static_cast<long long>(row) * top + k;
       const float v = expert_of[i] >= with_matrices ? to_float<T>(x[row * ldx + c])
                                                     : to_float<TY>(y[static_cast<long long>(pos_of[i]) * hidden + c]);
-      acc = fmaf(weight_of[i], v, acc);
+      acc = unit_weights ? acc + v : fmaf(weight_of[i], v, acc);
     }
     out[static_cast<long long>(row) * hidden + c] = from_float<T>(acc);
   }
@@ -447,10 +473,11 @@ __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restri
 using namespace pih;
 typedef __nv_bfloat16 bf16;
 
-// ints: expert_of[slots] | rank_of[slots] | pos_of[slots] | row_of[slots] | counts[experts] | plan[2 experts + 2];
+// ints: expert_of[slots] | rank_of[slots] | pos_of[slots] | row_of[slots] | counts[experts] | plan[2 experts + 2] |
+// slot_of[slots] (the (row, choice) slot at each position in expert order);
 // the caller zeroes counts.  weight_of: fp32 [slots].
 extern "C" long long pih_moe_route_words(int rows, int experts, int top) {
-  return 4LL * rows * top + experts + 2LL * experts + 2;
+  return 5LL * rows * top + experts + 2LL * experts + 2;
 }
 
 // grouped 0: only the choice and the weights (for the kernels that take every slot on its own; ints need no zeroing)
@@ -474,7 +501,7 @@ extern "C" int pih_moe_route(const void* logits, int rows, int experts, int top,
   PIH_LAUNCH_CHECK();
   launch_kernel(moe_scatter_kernel, dim3(static_cast<unsigned>((slots + 255) / 256)), dim3(256), 0, s,
                 static_cast<const int*>(expert_of), static_cast<const int*>(rank_of), static_cast<const int*>(plan),
-                static_cast<int>(slots), top, pos_of, row_of);
+                static_cast<int>(slots), top, pos_of, row_of, plan + 2 * experts + 2);
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -482,8 +509,8 @@ extern "C" int pih_moe_route(const void* logits, int rows, int experts, int top,
 // The same outputs as pih_moe_route from the scored routing (see moe_route_scored_kernel); logits fp32 [rows, ld] of which
 // the first ``experts`` columns are the router's outputs; correction fp32 [experts] or null.
 extern "C" int pih_moe_route_scored(const void* logits, long long ld, const void* correction, int rows, int experts, int top,
-                                    int groups, int keep, int renormalize, void* ints, void* weight_of, int grouped,
-                                    void* stream) {
+                                    int groups, int keep, int renormalize, int scoring, void* ints, void* weight_of,
+                                    int grouped, void* stream) {
   if (rows <= 0) return 0;
   if (experts < 1 || experts > 1024 || top < 1 || top > experts || groups < 1 || groups > 1024 || experts % groups ||
       keep < 1 || keep > groups)
@@ -498,7 +525,7 @@ extern "C" int pih_moe_route_scored(const void* logits, long long ld, const void
   int* plan = counts + experts;
   launch_kernel(moe_route_scored_kernel, dim3((rows + 3) / 4), dim3(128), 4 * 2 * groups * sizeof(float), s,
                 static_cast<const float*>(logits), ld, static_cast<const float*>(correction), rows, experts, top, groups,
-                keep, renormalize, expert_of, static_cast<float*>(weight_of), rank_of,
+                keep, renormalize, scoring, expert_of, static_cast<float*>(weight_of), rank_of,
                 grouped ? counts : static_cast<int*>(nullptr), pos_of);
   PIH_LAUNCH_CHECK();
   if (!grouped) return 0;
@@ -506,7 +533,7 @@ extern "C" int pih_moe_route_scored(const void* logits, long long ld, const void
   PIH_LAUNCH_CHECK();
   launch_kernel(moe_scatter_kernel, dim3(static_cast<unsigned>((slots + 255) / 256)), dim3(256), 0, s,
                 static_cast<const int*>(expert_of), static_cast<const int*>(rank_of), static_cast<const int*>(plan),
-                static_cast<int>(slots), top, pos_of, row_of);
+                static_cast<int>(slots), top, pos_of, row_of, plan + 2 * experts + 2);
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -516,11 +543,14 @@ extern "C" int pih_moe_route_scored(const void* logits, long long ld, const void
 // its own (the weight rows streamed with 16-byte loads) instead of the grouped product; needs hidden and ff to be
 // multiples of 8 (bf16) or 4 (32-bit) and hidden, ff <= 12288.  ``experts`` counts the router's outputs, of which the
 // last ``identity`` have no matrices: their output is the row of x itself.
+// ``gated`` 0: an expert is W_down max(W_up x, 0)^2 and w_gate_up is [experts, ff, hidden].  ``weigh_input`` 1: an expert
+// reads its row times the slot's weight (rounded to the storage type) and the outputs are summed as they are.
 extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const void* w_gate_up, const void* w_down, void* act,
                                void* y, void* out, const void* ints, const void* weight_of, int rows, int experts, int top,
-                               int hidden, int ff, int few_rows, int identity, void* stream) {
+                               int hidden, int ff, int few_rows, int identity, int gated, int weigh_input, void* stream) {
   if (rows <= 0) return 0;
   if (identity < 0 || identity > experts) return PIH_ERR_BAD_ARGUMENT;
+  if (weigh_input && identity > 0) return PIH_ERR_UNSUPPORTED;
   const int with_matrices = experts - identity;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long slots = static_cast<long long>(rows) * top;
@@ -528,45 +558,95 @@ extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const vo
   const int* pos_of = expert_of + 2 * slots;
   const int* row_of = pos_of + slots;
   const int* plan = row_of + slots + experts;
+  const int* slot_of = plan + 2 * experts + 2;
+  const float* in_w = weigh_input ? static_cast<const float*>(weight_of) : nullptr;
   const unsigned tiles = static_cast<unsigned>((slots + kMoeTile - 1) / kMoeTile + experts);
   if (tiles > 65535) return PIH_ERR_UNSUPPORTED;
-  const long long gu_stride = 2LL * ff * hidden, down_stride = static_cast<long long>(hidden) * ff;
+  const long long gu_stride = (gated ? 2LL : 1LL) * ff * hidden, down_stride = static_cast<long long>(hidden) * ff;
   if (few_rows) {
     const int vec = dtype == PIH_F32 ? 4 : 8;
     if (hidden % vec || ff % vec || hidden > 12288 || ff > 12288 || slots > 65535) return PIH_ERR_UNSUPPORTED;
   }
+#define PIH_MOE_FIRST(T, FORM)                                                                                         \
+  do {                                                                                                                 \
+    if (few_rows) {                                                                                                    \
+      launch_kernel(moe_gemv_kernel<T, T, FORM>, dim3(static_cast<unsigned>(slots), (ff + 31) / 32), dim3(256),        \
+                    hidden * sizeof(float), s, static_cast<const T*>(x), lda, top, expert_of, wgu,                     \
+                    wgu + static_cast<long long>(ff) * hidden, gu_stride, static_cast<T*>(act),                        \
+                    static_cast<long long>(ff), static_cast<const int*>(nullptr), with_matrices, ff, hidden, in_w);    \
+    } else {                                                                                                           \
+      launch_kernel(moe_grouped_kernel<T, T, FORM>, dim3((ff + 63) / 64, tiles), dim3(256), 0, s,                      \
+                    static_cast<const T*>(x), lda, row_of, wgu, wgu + static_cast<long long>(ff) * hidden, gu_stride,  \
+                    static_cast<T*>(act), static_cast<long long>(ff), plan, experts, with_matrices, ff, hidden, in_w,  \
+                    slot_of);                                                                                          \
+    }                                                                                                                  \
+  } while (0)
 #define PIH_MOE(T)                                                                                                     \
   do {                                                                                                                 \
     const T* wgu = static_cast<const T*>(w_gate_up);                                                                   \
+    if (gated) PIH_MOE_FIRST(T, 1); else PIH_MOE_FIRST(T, 2);                                                          \
+    PIH_LAUNCH_CHECK();                                                                                                \
     if (few_rows) {                                                                                                    \
-      launch_kernel(moe_gemv_kernel<T, T, true>, dim3(static_cast<unsigned>(slots), (ff + 31) / 32), dim3(256),        \
-                    hidden * sizeof(float), s, static_cast<const T*>(x), lda, top, expert_of, wgu,                     \
-                    wgu + static_cast<long long>(ff) * hidden, gu_stride, static_cast<T*>(act),                        \
-                    static_cast<long long>(ff), static_cast<const int*>(nullptr), with_matrices, ff, hidden);          \
-      PIH_LAUNCH_CHECK();                                                                                              \
-      launch_kernel(moe_gemv_kernel<T, float, false>, dim3(static_cast<unsigned>(slots), (hidden + 31) / 32),          \
+      launch_kernel(moe_gemv_kernel<T, float, 0>, dim3(static_cast<unsigned>(slots), (hidden + 31) / 32),              \
                     dim3(256), ff * sizeof(float), s, static_cast<const T*>(act), static_cast<long long>(ff), 1,       \
                     expert_of, static_cast<const T*>(w_down), static_cast<const T*>(nullptr), down_stride,             \
-                    static_cast<float*>(y), static_cast<long long>(hidden), pos_of, with_matrices, hidden, ff);        \
+                    static_cast<float*>(y), static_cast<long long>(hidden), pos_of, with_matrices, hidden, ff,         \
+                    static_cast<const float*>(nullptr));                                                               \
     } else {                                                                                                           \
-      launch_kernel(moe_grouped_kernel<T, T, true>, dim3((ff + 63) / 64, tiles), dim3(256), 0, s,                      \
-                    static_cast<const T*>(x), lda, row_of, wgu, wgu + static_cast<long long>(ff) * hidden, gu_stride,  \
-                    static_cast<T*>(act), static_cast<long long>(ff), plan, experts, with_matrices, ff, hidden);       \
-      PIH_LAUNCH_CHECK();                                                                                              \
-      launch_kernel(moe_grouped_kernel<T, float, false>, dim3((hidden + 63) / 64, tiles), dim3(256), 0, s,             \
+      launch_kernel(moe_grouped_kernel<T, float, 0>, dim3((hidden + 63) / 64, tiles), dim3(256), 0, s,                 \
                     static_cast<const T*>(act), static_cast<long long>(ff), static_cast<const int*>(nullptr),          \
                     static_cast<const T*>(w_down), static_cast<const T*>(nullptr), down_stride,                        \
-                    static_cast<float*>(y), static_cast<long long>(hidden), plan, experts, with_matrices, hidden, ff); \
+                    static_cast<float*>(y), static_cast<long long>(hidden), plan, experts, with_matrices, hidden, ff,  \
+                    static_cast<const float*>(nullptr), static_cast<const int*>(nullptr));                             \
     }                                                                                                                  \
     PIH_LAUNCH_CHECK();                                                                                                \
     launch_kernel(moe_combine_kernel<T, float>, dim3(rows), dim3(hidden >= 256 ? 256 : 128), 0, s,                     \
                   static_cast<const float*>(y), pos_of, static_cast<const float*>(weight_of), static_cast<T*>(out),    \
-                  rows, hidden, top, expert_of, with_matrices, static_cast<const T*>(x), lda);                         \
+                  rows, hidden, top, expert_of, with_matrices, static_cast<const T*>(x), lda, weigh_input);            \
   } while (0)
   if (dtype == PIH_F32) PIH_MOE(float);
   else if (dtype == PIH_BF16) PIH_MOE(bf16);
   else return PIH_ERR_BAD_ARGUMENT;
 #undef PIH_MOE
+#undef PIH_MOE_FIRST
+  PIH_LAUNCH_CHECK();
+  return 0;
+}
+
+// xs[pos] = round(x[row_of[pos]] * weight_of[slot_of[pos]]) for the positions of experts with matrices, in expert order:
+// what a library's grouped product reads when the weights multiply the experts' input.  xs [slots, hidden].
+namespace pih {
+template <typename T>
+__global__ void moe_gather_scaled_kernel(const T* __restrict__ x, long long ldx, const int* __restrict__ row_of,
+                                         const int* __restrict__ slot_of, const float* __restrict__ weight_of,
+                                         T* __restrict__ xs, int hidden) {
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long pos = blockIdx.x;
+  const float w = weight_of[slot_of[pos]];
+  const T* src = x + static_cast<long long>(row_of[pos]) * ldx;
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+    xs[pos * hidden + c] = from_float<T>(to_float<T>(src[c]) * w);
+}
+}  // namespace pih
+
+extern "C" int pih_moe_gather_scaled(int dtype, const void* x, long long ldx, const void* ints, const void* weight_of,
+                                     void* xs, int rows, int experts, int top, int hidden, void* stream) {
+  if (rows <= 0) return 0;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long long slots = static_cast<long long>(rows) * top;
+  const int* row_of = static_cast<const int*>(ints) + 3 * slots;
+  const int* slot_of = row_of + slots + experts + 2 * experts + 2;
+  if (dtype == PIH_BF16)
+    launch_kernel(moe_gather_scaled_kernel<bf16>, dim3(static_cast<unsigned>(slots)), dim3(hidden >= 1024 ? 256 : 128), 0, s,
+                  static_cast<const bf16*>(x), ldx, row_of, slot_of, static_cast<const float*>(weight_of),
+                  static_cast<bf16*>(xs), hidden);
+  else if (dtype == PIH_F32)
+    launch_kernel(moe_gather_scaled_kernel<float>, dim3(static_cast<unsigned>(slots)), dim3(hidden >= 1024 ? 256 : 128), 0, s,
+                  static_cast<const float*>(x), ldx, row_of, slot_of, static_cast<const float*>(weight_of),
+                  static_cast<float*>(xs), hidden);
+  else
+    return PIH_ERR_BAD_ARGUMENT;
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -574,14 +654,15 @@ extern "C" int pih_moe_experts(int dtype, const void* x, long long lda, const vo
 // out[row] = sum_k weight_of[row][k] * y[pos_of[row][k]] for y in bf16 (the output of a library's grouped product)
 // (x [rows, ldx] and with_matrices: see moe_combine_kernel)
 extern "C" int pih_moe_combine_bf16(const void* y, const void* ints, const void* weight_of, void* out, int rows, int top,
-                                    int hidden, int with_matrices, const void* x, long long ldx, void* stream) {
+                                    int hidden, int with_matrices, const void* x, long long ldx, int unit_weights,
+                                    void* stream) {
   if (rows <= 0) return 0;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int* expert_of = static_cast<const int*>(ints);
   const int* pos_of = expert_of + 2LL * rows * top;
   launch_kernel(moe_combine_kernel<bf16, bf16>, dim3(rows), dim3(hidden >= 256 ? 256 : 128), 0, s,
                 static_cast<const bf16*>(y), pos_of, static_cast<const float*>(weight_of), static_cast<bf16*>(out), rows,
-                hidden, top, expert_of, with_matrices, static_cast<const bf16*>(x), ldx);
+                hidden, top, expert_of, with_matrices, static_cast<const bf16*>(x), ldx, unit_weights);
   PIH_LAUNCH_CHECK();
   return 0;
 }

@@ -90,7 +90,7 @@ __global__ void add_gated_kernel(const T* __restrict__ a, const T* __restrict__ 
   const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (i >= rows * width) return;
   const long long row = i / width;
-  const float g = 1.0f / (1.0f + expf(-gate[row * ldg]));
+  const float g = gate != nullptr ? 1.0f / (1.0f + expf(-gate[row * ldg])) : 1.0f;      // no gate: a + b
   out[i] = from_float<T>(fmaf(g, to_float<T>(b[i]), to_float<T>(a[i])));
 }
 

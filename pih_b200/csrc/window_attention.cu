@@ -9,7 +9,9 @@
 //   out    = sum weight v, times sigmoid(gate[row][head]) where there is a gate
 //
 //   window_qk_prepare        per row: RMS norm over the WHOLE q (and k) projection with a weight a column, rotation of the
-//                            first columns of every head by a table of (cos, sin) in neighbouring pairs or in halves;
+//                            first columns of every head in neighbouring pairs or in halves, by a table of (cos, sin) or
+//                            by angles position * f_i computed in 32-bit from frequencies; without write_kv the rows
+//                            hold q alone and nothing goes to the cache (a mixer that reads another's keys and values);
 //                            q goes to a buffer of its own, k and v (v: its own columns, or the key columns as they
 //                            came, before norm and rotation) to the row's slot of the cache
 //   window_attention_generic a warp a (row, head): keys in chunks of 32 at multiples of 32 (a lane a key for the
@@ -82,7 +84,8 @@ __device__ __forceinline__ float element_of_words(const uint32_t (&w)[WORDS], in
 template <typename T>
 __global__ void __launch_bounds__(256)
 window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict__ q_out, const float* __restrict__ q_norm,
-                         const float* __restrict__ k_norm, float eps, const float* __restrict__ table, int rot,
+                         const float* __restrict__ k_norm, float eps, const float* __restrict__ table,
+                         const float* __restrict__ freq, int rot,
                          int interleaved, int max_positions, const int* __restrict__ positions,
                          const int* __restrict__ slot_mapping, T* __restrict__ cache, long long cache_slots, int heads,
                          int kv_heads, int dim, int vdim, int values_from_keys, uint32_t* __restrict__ error) {
@@ -121,13 +124,15 @@ window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict_
     pos = 0;
   }
   const float* cs = table != nullptr ? table + static_cast<long long>(pos) * rot : nullptr;   // (rot / 2) pairs of 2
+  const bool turns = rot > 0 && (cs != nullptr || freq != nullptr);
+  const float place = static_cast<float>(pos);
   const int half = rot >> 1;
   const T* xp = part == 0 ? x : x + nq;
   const int n = part == 0 ? nq : nk;
   const float* w = part == 0 ? q_norm : k_norm;
   T* dst = part == 0 ? q_out + row * nq : (slot >= 0 ? cache + slot * width : nullptr);
   if (dst == nullptr) return;
-  const bool pieces = aligned && dim % V == 0 && (cs == nullptr || (interleaved && rot % V == 0)) &&
+  const bool pieces = aligned && dim % V == 0 && (!turns || (interleaved && rot % V == 0)) &&
                       n <= static_cast<int>(blockDim.x) * V * kHeld;
   if (pieces) {
     float held[kHeld][V];
@@ -156,10 +161,12 @@ window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict_
 #pragma unroll
       for (int i = 0; i < V; ++i) o[i] = w != nullptr ? held[u][i] * inv * w[e + i] : held[u][i];
       const int c = e % dim;                                   // the piece lies inside a head, and inside or outside the rotation
-      if (cs != nullptr && c < rot) {
+      if (turns && c < rot) {
 #pragma unroll
         for (int i = 0; i < V; i += 2) {
-          const float cosine = cs[c + i], sine = cs[c + i + 1];   // pair (c + i) / 2
+          float cosine, sine;                                     // pair (c + i) / 2
+          if (cs != nullptr) { cosine = cs[c + i]; sine = cs[c + i + 1]; }
+          else sincosf(place * freq[(c + i) >> 1], &sine, &cosine);
           const float a = o[i], b = o[i + 1];
           o[i] = a * cosine - b * sine;
           o[i + 1] = b * cosine + a * sine;
@@ -186,14 +193,16 @@ window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict_
     const int c = e % dim;                                     // column within the head
     float o = to_float<T>(xp[e]);
     if (w != nullptr) o = o * inv * w[e];
-    if (cs != nullptr && c < rot) {
+    if (turns && c < rot) {
       int pair, other;
       bool first;                                              // whether e is the first number of its pair
       if (interleaved) { pair = c >> 1; first = (c & 1) == 0; other = first ? e + 1 : e - 1; }
       else { pair = c < half ? c : c - half; first = c < half; other = first ? e + half : e - half; }
       float p = to_float<T>(xp[other]);
       if (w != nullptr) p = p * inv * w[other];
-      const float cosine = cs[2 * pair], sine = cs[2 * pair + 1];
+      float cosine, sine;
+      if (cs != nullptr) { cosine = cs[2 * pair]; sine = cs[2 * pair + 1]; }
+      else sincosf(place * freq[pair], &sine, &cosine);
       o = first ? o * cosine - p * sine : o * cosine + p * sine;
     }
     dst[e] = from_float<T>(o);
@@ -759,22 +768,27 @@ typedef __nv_bfloat16 bf16;
 
 // src [rows, ld]: q [heads x dim] | k [kv_heads x dim] | v [kv_heads x vdim] (no v columns with values_from_keys: the
 // key columns as they are become the values); q_out [rows, heads x dim]; q_norm fp32 [heads x dim], k_norm fp32
-// [kv_heads x dim] or null; table fp32 [max_positions, rot / 2, 2] or null; cache [num_pages, page_size, kv_heads (dim + vdim)].
+// [kv_heads x dim] or null; table fp32 [max_positions, rot / 2, 2] or null, and then freq fp32 [rot / 2] or null (angles
+// computed from the position); cache [num_pages, page_size, kv_heads (dim + vdim)].  write_kv 0: the rows hold q alone and
+// nothing goes to the cache.
 extern "C" int pih_window_qk_prepare(int dtype, const void* src, long long ld, void* q_out, const void* q_norm,
-                                     const void* k_norm, float eps, const void* table, int rot, int interleaved,
-                                     int max_positions, const void* positions, const void* slot_mapping, void* cache,
-                                     int page_size, int num_pages, int rows, int heads, int kv_heads, int dim, int vdim,
-                                     int values_from_keys, void* error, void* stream) {
+                                     const void* k_norm, float eps, const void* table, const void* freq, int rot,
+                                     int interleaved, int max_positions, const void* positions, const void* slot_mapping,
+                                     void* cache, int page_size, int num_pages, int rows, int heads, int kv_heads, int dim,
+                                     int vdim, int values_from_keys, int write_kv, void* error, void* stream) {
   if (rows <= 0) return 0;
+  if (table != nullptr && freq != nullptr) return PIH_ERR_BAD_ARGUMENT;
   if (rot < 0 || rot > dim || (rot & 1) || heads < 1 || kv_heads < 1 || (values_from_keys && vdim != dim))
     return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long slots = static_cast<long long>(num_pages) * page_size;
   const int threads = heads * dim >= 1024 ? 256 : 128;
 #define PIH_WQK(T)                                                                                                     \
-  launch_kernel(window_qk_prepare_kernel<T>, dim3(rows, 3), dim3(threads), 0, s, static_cast<const T*>(src), ld,          \
+  launch_kernel(window_qk_prepare_kernel<T>, dim3(rows, write_kv ? 3 : 1), dim3(threads), 0, s,                        \
+                static_cast<const T*>(src), ld,                                                                        \
                 static_cast<T*>(q_out), static_cast<const float*>(q_norm), static_cast<const float*>(k_norm), eps,     \
-                static_cast<const float*>(rot > 0 ? table : nullptr), rot, interleaved, max_positions,                 \
+                static_cast<const float*>(rot > 0 ? table : nullptr), static_cast<const float*>(rot > 0 ? freq : nullptr), \
+                rot, interleaved, max_positions,                                                                       \
                 static_cast<const int*>(positions), static_cast<const int*>(slot_mapping), static_cast<T*>(cache), slots, \
                 heads, kv_heads, dim, vdim, values_from_keys, static_cast<uint32_t*>(error))
   if (dtype == PIH_F32) PIH_WQK(float);

@@ -98,7 +98,7 @@ class ModelRunner:
         self.cache = cache
         self.device = model.rt.device
         self.builder = BatchBuilder(self.device)
-        self.num_entries = len(model.spec.schedule)
+        self.num_entries = len(model.cache_needs())      # the schedule's entries and what the model itself keeps
         self.steps_run = 0
         # A decode step is captured when its shape (requests, table width) has been run this many times uncaptured.
         # A capture costs about as much as ten uncaptured steps; a batch whose requests end one after the other

@@ -111,7 +111,8 @@ class CudaOps:
                      "pih_stream_cast", "pih_stream_norm_add", "pih_bias_xielu", "pih_add_gated", "pih_retention",
                      "pih_diff_qk_prepare", "pih_diff_attention", "pih_diff_attention_tile_takes", "pih_moe_route_scored",
                      "pih_act_mul", "pih_embed_positions", "pih_hyper_stream", "pih_window_qk_prepare",
-                     "pih_window_attention", "pih_window_attention_tile_takes"):
+                     "pih_window_attention", "pih_window_attention_tile_takes", "pih_embed_bigram", "pih_rmsnorm_rows",
+                     "pih_rotate_heads", "pih_gate_mul", "pih_unary_act", "pih_scale_rows", "pih_moe_gather_scaled"):
             getattr(lib, name).restype = c_int
         lib.pih_attention_scratch_floats.restype = c_ll
         lib.pih_top_logprobs_scratch_words.restype = c_ll
@@ -730,13 +731,20 @@ class CudaOps:
         return out
 
     def latent_write(self, raw: torch.Tensor, weight: torch.Tensor, eps: float, cache: torch.Tensor,
-                     slot_mapping: torch.Tensor) -> None:
-        """``rmsnorm(raw) * weight`` of every row into its slot of the paged latent cache ``[pages, page_size, rank]``."""
-        T, rank = raw.shape
+                     slot_mapping: torch.Tensor, frequencies: Optional[torch.Tensor] = None, interleaved: bool = False,
+                     positions: Optional[torch.Tensor] = None) -> None:
+        """``rmsnorm(raw) * weight`` of every row into its slot of the paged latent cache ``[pages, page_size, rank]``.
+        With ``frequencies`` (fp32 ``[rot / 2]``) the rows hold ``rot`` more numbers behind the ``rank`` normed ones:
+        they are not normed but rotated by ``positions[row] * f_i`` (pairs of neighbours with ``interleaved``, else
+        halves) and cached behind the latent (the cache is ``rank + rot`` wide)."""
+        T, width = raw.shape
+        rot = 2 * frequencies.shape[0] if frequencies is not None else 0
+        rank = width - rot
         num_pages, page_size = cache.shape[0], cache.shape[1]
-        assert raw.stride(1) == 1 and cache.dtype == raw.dtype and cache.shape[2] == rank
+        assert raw.stride(1) == 1 and cache.dtype == raw.dtype and cache.shape[2] == width and weight.shape[0] == rank
         rc = self.lib.pih_latent_write(_DT[raw.dtype], _ptr(raw), c_ll(raw.stride(0)), _ptr(weight), c_float(eps),
-                                       _ptr(cache), _ptr(slot_mapping), T, rank, page_size, num_pages, self._err(),
+                                       _ptr(cache), _ptr(slot_mapping), T, rank, page_size, num_pages, rot,
+                                       1 if interleaved else 0, _ptr(frequencies), _ptr(positions), self._err(),
                                        self._stream())
         self._check(rc, "latent_write")
 
@@ -807,9 +815,15 @@ class CudaOps:
         ``routing`` selects the other router: scores are the softmax over all ``outputs`` (the first columns of
         ``logits``, whose rows may be longer), the choice goes by score plus ``correction`` within the
         ``groups_keep`` best of ``groups`` groups, the chosen weigh with their scores (``renormalize``: divided by
-        their sum), and the outputs behind the experts that have matrices are identity experts (the row itself)."""
+        their sum), and the outputs behind the experts that have matrices are identity experts (the row itself).
+        ``routing["scoring"]`` "sigmoid": a score is the sigmoid of the output's own logit.  ``routing["gated"]`` False:
+        an expert is ``W_down max(W_up x, 0)^2`` and ``w_gate_up`` is ``[experts, ff, hidden]``.  ``routing["weigh"]``
+        "input": an expert reads the row times its weight (rounded to the compute dtype) and the outputs are summed
+        as they are."""
         T, hidden = x.shape
-        with_matrices, ff = w_gate_up.shape[0], w_gate_up.shape[1] // 2
+        gated = routing.get("gated", True) if routing is not None else True
+        weigh_input = routing is not None and routing.get("weigh", "output") == "input"
+        with_matrices, ff = w_gate_up.shape[0], w_gate_up.shape[1] // (2 if gated else 1)
         experts = routing["outputs"] if routing is not None else with_matrices
         identity = experts - with_matrices
         assert logits.dtype == torch.float32 and logits.stride(1) == 1 and logits.shape[0] == T and identity >= 0
@@ -829,8 +843,9 @@ class CudaOps:
         else:
             rc = self.lib.pih_moe_route_scored(_ptr(logits), c_ll(logits.stride(0)), _ptr(routing.get("correction")), T,
                                                experts, top, int(routing.get("groups", 1)), int(routing.get("groups_keep", 1)),
-                                               1 if routing.get("renormalize") else 0, _ptr(ints), _ptr(weight_of),
-                                               0 if few else 1, self._stream())
+                                               1 if routing.get("renormalize") else 0,
+                                               {"softmax": 0, "sigmoid": 1}[routing.get("scoring", "softmax")], _ptr(ints),
+                                               _ptr(weight_of), 0 if few else 1, self._stream())
         self._check(rc, "moe_route")
         self.launches += 0 if few else 2
         out = torch.empty(T, hidden, dtype=x.dtype, device=x.device)
@@ -839,19 +854,26 @@ class CudaOps:
             row_of = ints[3 * slots:4 * slots]
             ends = ints[4 * slots + experts + 1:4 * slots + experts + 1 + with_matrices]   # where each expert's rows end
             # (the rows of identity experts lie behind the last of these: the grouped products leave them alone)
-            xs = self.gather_rows(x, row_of) if x.is_contiguous() else x.index_select(0, row_of)
-            gate_up = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)     # [slots, 2 ff]
-            act = self.silu_mul(gate_up)
+            if weigh_input:
+                xs = torch.empty(slots, hidden, dtype=x.dtype, device=x.device)
+                rc = self.lib.pih_moe_gather_scaled(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(ints), _ptr(weight_of),
+                                                    _ptr(xs), T, experts, top, hidden, self._stream())
+                self._check(rc, "moe_gather_scaled")
+            else:
+                xs = self.gather_rows(x, row_of) if x.is_contiguous() else x.index_select(0, row_of)
+            gate_up = torch._grouped_mm(xs, w_gate_up.transpose(1, 2), offs=ends)     # [slots, 2 ff] (or [slots, ff])
+            act = self.silu_mul(gate_up) if gated else self.activation(gate_up, "relu2")
             y = torch._grouped_mm(act, w_down.transpose(1, 2), offs=ends)             # [slots, hidden]
             rc = self.lib.pih_moe_combine_bf16(_ptr(y), _ptr(ints), _ptr(weight_of), _ptr(out), T, top, hidden,
-                                               with_matrices, _ptr(x), c_ll(x.stride(0)), self._stream())
+                                               with_matrices, _ptr(x), c_ll(x.stride(0)), 1 if weigh_input else 0,
+                                               self._stream())
             self._check(rc, "moe_combine")
             return out
         act = torch.empty(slots, ff, dtype=x.dtype, device=x.device)
         y = torch.empty(slots, hidden, dtype=torch.float32, device=x.device)
         rc = self.lib.pih_moe_experts(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(w_gate_up), _ptr(w_down), _ptr(act),
                                       _ptr(y), _ptr(out), _ptr(ints), _ptr(weight_of), T, experts, top, hidden, ff,
-                                      1 if few else 0, identity, self._stream())
+                                      1 if few else 0, identity, 1 if gated else 0, 1 if weigh_input else 0, self._stream())
         self._check(rc, "moe_experts")
         self.launches += 2
         return out
@@ -893,12 +915,12 @@ class CudaOps:
         return out
 
     def add_gated(self, a: torch.Tensor, b: torch.Tensor, gate: torch.Tensor) -> torch.Tensor:
-        """``a + sigmoid(gate[row]) * b``: a, b ``[T, width]``; gate fp32 ``[T]`` (a view of logits)."""
+        """``a + sigmoid(gate[row]) * b``: a, b ``[T, width]``; gate fp32 ``[T]`` (a view of logits), or None: ``a + b``."""
         rows, width = a.shape
-        assert a.is_contiguous() and b.is_contiguous() and b.shape == a.shape and gate.dtype == torch.float32
+        assert a.is_contiguous() and b.is_contiguous() and b.shape == a.shape and (gate is None or gate.dtype == torch.float32)
         out = torch.empty_like(a)
-        rc = self.lib.pih_add_gated(_DT[a.dtype], _ptr(a), _ptr(b), _ptr(gate), c_ll(gate.stride(0)), _ptr(out), c_ll(rows),
-                                    width, self._stream())
+        rc = self.lib.pih_add_gated(_DT[a.dtype], _ptr(a), _ptr(b), _ptr(gate), c_ll(gate.stride(0) if gate is not None else 0),
+                                    _ptr(out), c_ll(rows), width, self._stream())
         self._check(rc, "add_gated")
         return out
 
@@ -1017,23 +1039,31 @@ class CudaOps:
     # -- attention over a window with a sink --------------------------------------------------------------------------
     def window_qk_prepare(self, src: torch.Tensor, *, q_norm, k_norm, eps: float, rope_table, rotary_dim: int,
                           interleaved: bool, positions, slot_mapping, cache: torch.Tensor, heads: int, kv_heads: int,
-                          key_dim: int, value_dim: int, values_from_keys: bool) -> torch.Tensor:
+                          key_dim: int, value_dim: int, values_from_keys: bool,
+                          frequencies: Optional[torch.Tensor] = None, write_kv: bool = True) -> torch.Tensor:
         """Rows ``[q: heads x key_dim | k: kv_heads x key_dim | v: kv_heads x value_dim]`` (no v columns with
         ``values_from_keys``: the values are the key columns as they come).  q and k are RMS-normed over their whole
         width (fp32 weights a column, or None) and rotated by ``rope_table`` (fp32 ``[positions, rotary_dim / 2,
         2]``, pairs of neighbours with ``interleaved``, else halves); q is returned as ``[T, heads x key_dim]``, k and v
-        go to the rows' slots of ``cache [pages, page_size, kv_heads (key_dim + value_dim)]``."""
+        go to the rows' slots of ``cache [pages, page_size, kv_heads (key_dim + value_dim)]``.  ``frequencies`` (fp32
+        ``[rotary_dim / 2]``) in the table's place: the angles ``position * f_i`` are formed in 32-bit in the kernel.
+        ``write_kv`` False: the rows hold q alone and nothing goes to the cache."""
         rows = src.shape[0]
         num_pages, page_size, width = cache.shape
         assert src.stride(1) == 1 and cache.dtype == src.dtype and width == kv_heads * (key_dim + value_dim)
-        assert src.shape[1] >= heads * key_dim + kv_heads * key_dim + (0 if values_from_keys else kv_heads * value_dim)
+        assert src.shape[1] >= heads * key_dim + (0 if not write_kv else
+                                                   kv_heads * key_dim + (0 if values_from_keys else kv_heads * value_dim))
+        assert rope_table is None or frequencies is None
         q = torch.empty(rows, heads * key_dim, dtype=src.dtype, device=src.device)
-        rot = rotary_dim if rope_table is not None else 0
+        rot = rotary_dim if (rope_table is not None or frequencies is not None) else 0
+        assert frequencies is None or 2 * frequencies.shape[0] == rot
         rc = self.lib.pih_window_qk_prepare(_DT[src.dtype], _ptr(src), c_ll(src.stride(0)), _ptr(q), _ptr(q_norm),
-                                            _ptr(k_norm), c_float(eps), _ptr(rope_table), rot, 1 if interleaved else 0,
+                                            _ptr(k_norm), c_float(eps), _ptr(rope_table), _ptr(frequencies), rot,
+                                            1 if interleaved else 0,
                                             rope_table.shape[0] if rope_table is not None else 0, _ptr(positions),
                                             _ptr(slot_mapping), _ptr(cache), page_size, num_pages, rows, heads, kv_heads,
-                                            key_dim, value_dim, 1 if values_from_keys else 0, self._err(), self._stream())
+                                            key_dim, value_dim, 1 if values_from_keys else 0, 1 if write_kv else 0,
+                                            self._err(), self._stream())
         self._check(rc, "window_qk_prepare")
         return q
 
@@ -1084,3 +1114,75 @@ class CudaOps:
         return out
 
     window_attention_fast = True           # False: bf16 steps use the in-order warp kernel too
+
+    # -- a bigram embedding, rotations by computed angles, gates a column, two-matrix experts -----------------------------
+    def embed_bigram(self, table: torch.Tensor, bigram: torch.Tensor, step, *, state: torch.Tensor, mul_prev: int,
+                     mul_cur: int, buckets: int, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """``table[token] + bigram[(previous * mul_prev + token * mul_cur) mod buckets]`` for the step's rows, summed in
+        32-bit; a sequence's first token takes ``bigram[buckets]``.  The token before a request's first row of the
+        step comes from ``state[slot]`` (int32 ``[slots, 1]``), where the kernel leaves the step's last token."""
+        rows, (vocab, width) = step.token_ids.shape[0], table.shape
+        out_dtype = out_dtype or table.dtype
+        assert table.is_contiguous() and bigram.is_contiguous() and bigram.shape == (buckets + 1, width)
+        assert bigram.dtype == table.dtype and state.dtype == torch.int32
+        out = torch.empty(rows, width, dtype=out_dtype, device=table.device)
+        rc = self.lib.pih_embed_bigram(_DT[table.dtype], _DT[out_dtype], _ptr(table), _ptr(bigram), _ptr(step.token_ids),
+                                       _ptr(step.positions), _ptr(step.request_of_row), _ptr(step.cu_q),
+                                       _ptr(step.state_slots), _ptr(state), c_ll(state.stride(0)), state.shape[0], _ptr(out),
+                                       rows, width, vocab, c_ll(buckets), c_ll(mul_prev), c_ll(mul_cur), self._err(),
+                                       self._stream())
+        self._check(rc, "embed_bigram")
+        return out
+
+    def rmsnorm_rows(self, x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+        """``x / sqrt(mean(x^2) + eps) * weight`` over the columns of ``x [T, n]`` (a view whose rows may be strided),
+        ``weight`` fp32 ``[n]``; returns ``[T, n]`` contiguous in the dtype of ``x``."""
+        T, n = x.shape
+        assert x.stride(1) == 1 and weight.dtype == torch.float32 and weight.shape[0] == n
+        out = torch.empty(T, n, dtype=x.dtype, device=x.device)
+        rc = self.lib.pih_rmsnorm_rows(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(weight), _ptr(out), T, n, c_float(eps),
+                                       self._stream())
+        self._check(rc, "rmsnorm_rows")
+        return out
+
+    def rotate_heads(self, x: torch.Tensor, *, offset: int, frequencies: torch.Tensor, interleaved: bool,
+                     positions: torch.Tensor) -> torch.Tensor:
+        """``x [T, heads, width]`` (a view whose rows may be strided) with the columns ``offset .. offset + rot`` of
+        every head rotated by ``positions[row] * f_i`` (32-bit angles; ``rot = 2 len(frequencies)``; pairs of neighbours
+        with ``interleaved``, else halves); returns ``[T, heads, width]`` contiguous."""
+        T, heads, width = x.shape
+        assert x.stride(2) == 1 and x.stride(1) == width and frequencies.dtype == torch.float32
+        out = torch.empty(T, heads, width, dtype=x.dtype, device=x.device)
+        rc = self.lib.pih_rotate_heads(_DT[x.dtype], _ptr(x), c_ll(x.stride(0)), _ptr(out), _ptr(frequencies), _ptr(positions),
+                                       T, heads, width, offset, 2 * frequencies.shape[0], 1 if interleaved else 0,
+                                       self._stream())
+        self._check(rc, "rotate_heads")
+        return out
+
+    def gate_mul(self, a: torch.Tensor, gate: torch.Tensor, kind: str = "sigmoid") -> torch.Tensor:
+        """``a * sigmoid(gate)`` (``kind`` "silu": ``a * silu(gate)``), column by column: a ``[T, n]`` contiguous, gate
+        ``[T, n]`` (a view whose rows may be strided); 32-bit inside, rounded once."""
+        T, n = a.shape
+        assert a.is_contiguous() and gate.shape == a.shape and gate.stride(1) == 1 and gate.dtype == a.dtype
+        out = torch.empty_like(a)
+        rc = self.lib.pih_gate_mul(_DT[a.dtype], _ptr(a), _ptr(gate), c_ll(gate.stride(0)), _ptr(out), c_ll(T), n,
+                                   {"sigmoid": 1, "silu": 2}[kind], self._stream())
+        self._check(rc, "gate_mul")
+        return out
+
+    def activation(self, z: torch.Tensor, kind: str) -> torch.Tensor:
+        """``kind`` "relu2": the square of ``max(z, 0)``; z ``[T, n]`` (rows may be strided); 32-bit inside, rounded once."""
+        T, n = z.shape
+        assert z.stride(1) == 1
+        out = torch.empty(T, n, dtype=z.dtype, device=z.device)
+        rc = self.lib.pih_unary_act(_DT[z.dtype], _ptr(z), c_ll(z.stride(0)), _ptr(out), c_ll(T), n, {"relu2": 1}[kind],
+                                    self._stream())
+        self._check(rc, "unary_act")
+        return out
+
+    def scale_(self, x: torch.Tensor, scale: float) -> torch.Tensor:
+        """``x *= scale`` in place; x fp32, contiguous."""
+        assert x.dtype == torch.float32 and x.is_contiguous()
+        rc = self.lib.pih_scale_rows(_ptr(x), c_ll(x.numel()), c_float(scale), self._stream())
+        self._check(rc, "scale_rows")
+        return x

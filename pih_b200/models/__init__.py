@@ -20,7 +20,7 @@ import torch
 from ..config.registry import load_config
 from ..config.specs import ModelSpec
 from ..parts import part_class
-from ..parts.registry import Runtime, TensorInfo
+from ..parts.registry import Runtime, StateNeed, TensorInfo
 from ..parts._bind import bind_matrix
 from ..weights.loader import load_weights, tensor_shapes
 
@@ -30,6 +30,8 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, TensorInfo]:
     out = {spec.embed_name: TensorInfo((spec.vocab, spec.hidden))}
     if spec.position_name is not None:
         out[spec.position_name] = TensorInfo((spec.max_positions, spec.hidden))
+    if spec.bigram is not None:
+        out[spec.bigram.name] = TensorInfo((spec.bigram.buckets + 1, spec.hidden))
     for block in spec.blocks:
         cls = part_class("block", block.arrangement)
         for rel, info in cls.expected_tensors(block).items():
@@ -50,6 +52,9 @@ class CausalLM:
         self.embed = bind_matrix(weights[spec.embed_name], rt)
         self.head = self.embed if spec.tie_embeddings else bind_matrix(weights[spec.head_name], rt)
         self.places = bind_matrix(weights[spec.position_name], rt) if spec.position_name is not None else None
+        self.bigram = bind_matrix(weights[spec.bigram.name], rt) if spec.bigram is not None else None
+        if self.bigram is not None and (spec.streams or self.places is not None):
+            raise ValueError("a bigram embedding goes with one residual stream and no table of places")
         self._ones = torch.ones(spec.streams, dtype=torch.float32, device=rt.device) if spec.streams else None
         self.blocks = []
         for block in spec.blocks:
@@ -70,12 +75,17 @@ class CausalLM:
 
     # -- what the cache manager must provide, per schedule entry -------------
     def cache_needs(self) -> List[Optional[object]]:
+        """One need a schedule entry and, behind them, what the model itself keeps per request: with a bigram
+        embedding the request's last token (one int32 in its state slot; the step function hands the model a
+        view for every need, in this order)."""
         needs = []
         for entry in self.spec.schedule:
             if entry.reads_cache_of is not None:
                 needs.append(None)
             else:
                 needs.append(self.blocks[entry.layer].mixer.cache_need())
+        if self.bigram is not None:
+            needs.append(StateNeed((1,), torch.int32))
         return needs
 
     # -- one pass over the rows of a step --------------------------------------
@@ -85,7 +95,14 @@ class CausalLM:
         or None when no logits are wanted."""
         ops = self.rt.ops
         wide = self.spec.stream_dtype == "float32" and self.rt.dtype != torch.float32
-        if self.spec.streams:
+        if self.bigram is not None:
+            # the token's row plus the row of the pair (previous token, token); the request's last token is read from
+            # and left in its state slot, so a portion or a decoded token finds the token before it
+            b = self.spec.bigram
+            h = ops.embed_bigram(self.embed, self.bigram, step, state=caches[len(self.spec.schedule)].state,
+                                 mul_prev=b.mul_prev, mul_cur=b.mul_cur, buckets=b.buckets,
+                                 out_dtype=torch.float32 if wide else self.rt.dtype)
+        elif self.spec.streams:
             # several residual streams, 32-bit, all equal to the embedding at the start; ``delta`` is the last
             # sub-layer's output with the coefficients that write it into the streams
             h = ops.embed_positions(self.embed, self.places, step.token_ids, step.positions, streams=self.spec.streams)
@@ -108,7 +125,10 @@ class CausalLM:
                                   eps=self.final_norm.spec.eps, rows=step.logit_rows, out_dtype=self.rt.dtype)
         else:
             xn = self.final_norm.add_forward(h, delta, rows=step.logit_rows)
-        return ops.linear(xn, self.head, out_dtype=torch.float32)
+        logits = ops.linear(xn, self.head, out_dtype=torch.float32)
+        if self.spec.logit_scale != 1.0:
+            ops.scale_(logits, self.spec.logit_scale)
+        return logits
 
 
 def load_model(model_dir: str, rt: Runtime):

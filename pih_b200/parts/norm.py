@@ -23,12 +23,16 @@ class RMSNorm:
 
     @classmethod
     def expected_tensors(cls, spec):
-        return {getattr(spec, "weight_name", "weight"): TensorInfo((spec.width,), "one_plus_normal")}
+        init = "normal" if getattr(spec, "offset", 0.0) else "one_plus_normal"
+        return {getattr(spec, "weight_name", "weight"): TensorInfo((spec.width,), init)}
 
     def __init__(self, spec, weights, rt: Runtime):
         self.spec = spec
         self.rt = rt
         self.weight = bind_vector(weights[getattr(spec, "weight_name", "weight")], rt)
+        if getattr(spec, "offset", 0.0):
+            # a weight stored around zero: ``offset + w`` multiplies, formed once in 32-bit
+            self.weight = (self.weight.float() + float(spec.offset)).contiguous()
         self._weight_f32 = None
 
     @property

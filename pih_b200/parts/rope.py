@@ -49,7 +49,10 @@ class RotaryEncoding:
 class ComputedRotary:
     """The same rotate-half rotation without a table: the mixer's kernel forms ``angle = position * f_i`` in 32-bit
     from the frequencies ``f_i = theta^(-2i/rotary_dim)`` (computed in double here, rounded once) and takes its
-    cosine and sine there.  No longest context has to be known."""
+    cosine and sine there.  No longest context has to be known.  ``interleaved``: the pairs are neighbours instead of
+    halves.  With ``stretch`` = (factor, low, high, original) the slow pairs are slowed down: with ``turns_i = original
+    f_i / (2 pi)`` and ``t_i = clamp((turns_i - low) / (high - low), 0, 1)`` the frequency is ``f_i (t_i + (1 - t_i) /
+    factor)``."""
 
     @classmethod
     def expected_tensors(cls, spec):
@@ -60,9 +63,24 @@ class ComputedRotary:
             raise ValueError(f"rotary_dim must be even and within head_dim, got {spec.rotary_dim}")
         self.spec = spec
         self.rotary_dim = spec.rotary_dim
+        self.interleaved = bool(getattr(spec, "interleaved", False))
+        self._frequencies = self.frequencies_of(spec).to(torch.float32).to(rt.device).contiguous()
+
+    @staticmethod
+    def frequencies_of(spec) -> torch.Tensor:
+        """float64 [rotary_dim / 2]."""
+        import math
         pair = torch.arange(spec.rotary_dim // 2, dtype=torch.float64)
-        inv = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * pair / spec.rotary_dim)
-        self._frequencies = inv.to(torch.float32).to(rt.device).contiguous()
+        f = torch.pow(torch.tensor(float(spec.theta), dtype=torch.float64), -2.0 * pair / spec.rotary_dim)
+        stretch = getattr(spec, "stretch", None)
+        if stretch is None:
+            return f
+        factor, low, high, original = (float(v) for v in stretch)
+        if factor <= 0 or original <= 0 or low <= 0 or high <= 0 or low == high:
+            raise ValueError("stretched rotation: factor, low, high and original must be positive, low and high differ")
+        turns = original * f / (2.0 * math.pi)
+        t = torch.clamp((turns - low) / (high - low), 0.0, 1.0)
+        return f * (t + (1.0 - t) / factor)
 
     def rotation_table(self):
         return None

@@ -17,6 +17,12 @@ window, so the kernels index it by the distance itself); capped scores; the gate
 The cache holds ONE vector per token, ``[k: kv_heads x key_dim | v: kv_heads x value_dim]`` after norm and rotation
 (``PagedVectorNeed`` with the window and the kept first tokens: the pages between them go back to the pool).  Scores,
 softmax, sink and gate are 32-bit whatever the compute dtype.
+
+A mixer built with ``own_kv`` False has no key/value tensors: its schedule entry reads another entry's cache, with
+queries, window, sink and output projection of its own.  The entry that keeps the cache holds it as far back as
+``cache_window`` says (the widest window of those that read it).  The rotation comes from a table of cosines and
+sines per position or, from a position part that computes its angles, from frequencies: ``position * f_i`` in 32-bit
+inside the kernel.
 """
 from __future__ import annotations
 
@@ -52,17 +58,21 @@ class WindowAttention:
     @classmethod
     def expected_tensors(cls, spec):
         n = spec.names
-        out = {n["q"]: TensorInfo((spec.q_size, spec.hidden)), n["k"]: TensorInfo((spec.k_size, spec.hidden)),
-               n["o"]: TensorInfo((spec.hidden, spec.heads * spec.value_dim))}
-        if not spec.values_from_keys:
+        own = getattr(spec, "own_kv", True)
+        out = {n["q"]: TensorInfo((spec.q_size, spec.hidden)), n["o"]: TensorInfo((spec.hidden, spec.heads * spec.value_dim))}
+        if own:
+            out[n["k"]] = TensorInfo((spec.k_size, spec.hidden))
+        if own and not spec.values_from_keys:
             out[n["v"]] = TensorInfo((spec.v_size, spec.hidden))
         if spec.norm_eps is not None:
             out[n["q_norm"]] = TensorInfo((spec.q_size,), "one_plus_normal")
-            out[n["k_norm"]] = TensorInfo((spec.k_size,), "one_plus_normal")
+            if own:
+                out[n["k_norm"]] = TensorInfo((spec.k_size,), "one_plus_normal")
         if spec.conv_taps > 0:
             out[n["q_conv"]] = TensorInfo((spec.q_size, spec.conv_taps), "conv")
-            out[n["k_conv"]] = TensorInfo((spec.k_size, spec.conv_taps), "conv")
-            if not spec.values_from_keys:
+            if own:
+                out[n["k_conv"]] = TensorInfo((spec.k_size, spec.conv_taps), "conv")
+            if own and not spec.values_from_keys:
                 out[n["v_conv"]] = TensorInfo((spec.v_size, spec.conv_taps), "conv")
         if spec.bias_rows > 0:
             out[n["bias"]] = TensorInfo((spec.bias_rows, spec.heads), "unit_normal")
@@ -84,11 +94,12 @@ class WindowAttention:
         if spec.bias_rows > 0 and (spec.bias_rows < 2 or spec.bias_far <= spec.bias_rows // 2):
             raise ValueError("a bias by distance needs at least 2 rows and a far distance beyond half of them")
         self.spec, self.rt = spec, rt
+        self.own_kv = own = getattr(spec, "own_kv", True)
         n = spec.names
         f32 = dict(device=rt.device, dtype=torch.float32)
         # one product for everything that reads the block's input: [q | k | v | gate]
-        parts = [weights[n["q"]], weights[n["k"]]]
-        if not spec.values_from_keys:
+        parts = [weights[n["q"]]] + ([weights[n["k"]]] if own else [])
+        if own and not spec.values_from_keys:
             parts.append(weights[n["v"]])
         self.channels = sum(p.shape[0] for p in parts)
         if spec.head_gate:
@@ -97,12 +108,13 @@ class WindowAttention:
         self.w_o = bind_matrix(weights[n["o"]], rt)
         self.w_conv = None
         if spec.conv_taps > 0:
-            conv = [weights[n["q_conv"]], weights[n["k_conv"]]] + ([] if spec.values_from_keys else [weights[n["v_conv"]]])
+            conv = [weights[n["q_conv"]]] + ([weights[n["k_conv"]]] if own else []) + (
+                [weights[n["v_conv"]]] if own and not spec.values_from_keys else [])
             self.w_conv = bind_matrix(torch.cat(conv, dim=0), rt)
         self.q_norm = self.k_norm = None
         if spec.norm_eps is not None:
             self.q_norm = weights[n["q_norm"]].to(**f32).contiguous()
-            self.k_norm = weights[n["k_norm"]].to(**f32).contiguous()
+            self.k_norm = weights[n["k_norm"]].to(**f32).contiguous() if own else None
         self.bias = None
         if spec.bias_rows > 0:
             # beyond ``bias_far`` every distance has the last row; inside a window no distance reaches the window's size
@@ -117,23 +129,28 @@ class WindowAttention:
         self.position = None
         if spec.position is not None:
             self.position = part_class("position", spec.position.kind)(spec.position, {}, rt)
-            if self.position.rotation_table() is None:
-                raise TypeError("window attention rotates by a table of cosines and sines per position")
+            if self.position.rotation_table() is None and not hasattr(self.position, "frequencies"):
+                raise TypeError("window attention rotates by a table of cosines and sines per position or by frequencies")
 
     def _state_numbers(self) -> int:
         return max(self.spec.conv_taps - 1, 0) * self.channels
 
     def cache_need(self):
         s = self.spec
-        paged = PagedVectorNeed(s.k_size + s.v_size, s.window or None, s.keep_first if s.window else 0)
+        reach = getattr(s, "cache_window", None)
+        reach = s.window if reach is None else reach            # (0: every key stays)
+        paged = PagedVectorNeed(s.k_size + s.v_size, reach or None, s.keep_first if reach else 0) if self.own_kv else None
         if self._state_numbers() == 0:
             return paged
+        if paged is None:
+            return StateNeed((self._state_numbers(),), torch.float32)
         return PagedStateNeed(paged, StateNeed((self._state_numbers(),), torch.float32))
 
     def forward(self, x, step, cache):
         s, ops = self.spec, self.rt.ops
-        if not cache.writable:
-            raise ValueError("window attention keeps a cache of its own")
+        if cache.writable != self.own_kv:
+            raise ValueError("window attention: the schedule entry's cache does not fit the mixer "
+                             "(a mixer without keys and values reads another entry's cache, and only such a mixer)")
         proj = ops.linear(x, self.w_in)                      # [T, q | k | v | gate]
         gate = proj[:, self.channels:] if s.head_gate else None
         src = proj
@@ -141,12 +158,17 @@ class WindowAttention:
             state = cache.state if self._state_numbers() else proj.new_zeros((1, 1), dtype=torch.float32)
             src = ops.causal_conv(proj[:, :self.channels], self.w_conv, step=step, state=state, state_offset=0)
         table = self.position.rotation_table() if self.position is not None else None
+        rotation = {}
+        if self.position is not None and table is None:
+            rotation = dict(frequencies=self.position.frequencies())
+        if not self.own_kv:
+            rotation["write_kv"] = False
         geometry = dict(heads=s.heads, kv_heads=s.kv_heads, key_dim=s.key_dim, value_dim=s.value_dim)
         q = ops.window_qk_prepare(src, q_norm=self.q_norm, k_norm=self.k_norm, eps=s.norm_eps or 0.0, rope_table=table,
                                   rotary_dim=self.position.rotary_dim if self.position is not None else 0,
                                   interleaved=getattr(self.position, "interleaved", False), positions=step.positions,
                                   slot_mapping=cache.slot_mapping, cache=cache.kv, values_from_keys=s.values_from_keys,
-                                  **geometry)
+                                  **geometry, **rotation)
         attn = ops.window_attention(q, cache=cache.kv, block_table=cache.block_table, step=step, scale=s.scale,
                                     window=s.window, keep_first=s.keep_first, softcap=s.softcap or 0.0, bias=self.bias,
                                     sink=self.sink, gate=gate, **geometry)

@@ -244,9 +244,26 @@ class FakeOps:
                 out[t] = (S * y[t]).to(u.dtype)
         return out
 
-    def latent_write(self, raw, weight, eps, cache, slot_mapping):
-        v = raw.float()
+    @staticmethod
+    def _turn(x, positions, frequencies, interleaved):
+        """x [T, ..., rot]: every number of the last axis rotated, rot = 2 len(frequencies)."""
+        rot = 2 * frequencies.shape[0]
+        ang = positions.float()[:, None] * frequencies[None, :]
+        shape = [x.shape[0]] + [1] * (x.dim() - 2) + [rot // 2]
+        c, s = torch.cos(ang).reshape(shape), torch.sin(ang).reshape(shape)
+        if interleaved:
+            a, b = x[..., 0::2], x[..., 1::2]
+            return torch.stack([a * c - b * s, b * c + a * s], dim=-1).reshape(x.shape)
+        a, b = x[..., :rot // 2], x[..., rot // 2:]
+        return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
+
+    def latent_write(self, raw, weight, eps, cache, slot_mapping, frequencies=None, interleaved=False, positions=None):
+        rot = 2 * frequencies.shape[0] if frequencies is not None else 0
+        rank = raw.shape[1] - rot
+        v = raw[:, :rank].float()
         c = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight
+        if rot:
+            c = torch.cat([c, self._turn(raw[:, rank:].float(), positions, frequencies, interleaved)], dim=-1)
         flat = cache.view(-1, cache.shape[-1])
         for t, slot in enumerate(slot_mapping.tolist()):
             if slot == -2:
@@ -282,7 +299,10 @@ class FakeOps:
     @staticmethod
     def _scored_choice(logits, top, routing):
         n = routing["outputs"]
-        s = torch.softmax(logits[:, :n].float(), dim=-1)
+        if routing.get("scoring", "softmax") == "sigmoid":
+            s = torch.sigmoid(logits[:, :n].float())
+        else:
+            s = torch.softmax(logits[:, :n].float(), dim=-1)
         c = s + (routing["correction"] if routing.get("correction") is not None else 0.0)
         groups, keep = routing.get("groups", 1), routing.get("groups_keep", 1)
         if groups > 1:
@@ -295,6 +315,20 @@ class FakeOps:
         return idx, wt / wt.sum(-1, keepdim=True) if routing.get("renormalize") else wt
 
     def moe_experts(self, x, logits, w_gate_up, w_down, top, routing=None):
+        if routing is not None and not routing.get("gated", True):
+            # two-matrix experts around the squared ReLU; the weight on what the expert reads or on what it gives
+            idx, wt = self._scored_choice(logits, top, routing)
+            out = torch.zeros(x.shape, dtype=torch.float32)
+            xf = x.float()
+            on_input = routing.get("weigh", "output") == "input"
+            for t in range(x.shape[0]):
+                for j in range(top):
+                    e = int(idx[t, j])
+                    row = (xf[t] * wt[t, j]).to(x.dtype).float() if on_input else xf[t]
+                    a = torch.relu((row @ w_gate_up[e].float().T).to(x.dtype).float()) ** 2
+                    y = a.to(x.dtype).float() @ w_down[e].float().T
+                    out[t] += y if on_input else wt[t, j] * y
+            return out.to(x.dtype)
         ff = w_gate_up.shape[1] // 2
         w_gate, w_up = w_gate_up[:, :ff], w_gate_up[:, ff:]
         if routing is not None:
@@ -337,6 +371,8 @@ class FakeOps:
         return v.to(z.dtype)
 
     def add_gated(self, a, b, gate):
+        if gate is None:
+            return (a.float() + b.float()).to(a.dtype)
         return (a.float() + torch.sigmoid(gate)[:, None] * b.float()).to(a.dtype)
 
     @staticmethod
@@ -446,7 +482,7 @@ class FakeOps:
         return u.to(out_dtype or torch.float32)
 
     def window_qk_prepare(self, src, *, q_norm, k_norm, eps, rope_table, rotary_dim, interleaved, positions, slot_mapping,
-                          cache, heads, kv_heads, key_dim, value_dim, values_from_keys):
+                          cache, heads, kv_heads, key_dim, value_dim, values_from_keys, frequencies=None, write_kv=True):
         T = src.shape[0]
         nq, nk, nv = heads * key_dim, kv_heads * key_dim, kv_heads * value_dim
 
@@ -465,9 +501,13 @@ class FakeOps:
                     half = rotary_dim // 2
                     a, b = x[..., :half].clone(), x[..., half:rotary_dim].clone()
                     x[..., :half], x[..., half:rotary_dim] = a * c - b * s, b * c + a * s
+            elif frequencies is not None:
+                x[..., :rotary_dim] = self._turn(x[..., :rotary_dim].clone(), positions, frequencies, interleaved)
             return x.reshape(T, -1)
 
         q = prepared(src[:, :nq], q_norm).to(src.dtype)
+        if not write_kv:
+            return q
         k = prepared(src[:, nq:nq + nk], k_norm).to(src.dtype)
         v = src[:, nq:nq + nk] if values_from_keys else src[:, nq + nk:nq + nk + nv]
         flat = cache.view(-1, cache.shape[-1])
@@ -516,3 +556,40 @@ class FakeOps:
                     o = o * torch.sigmoid(gate[t, h].float())
                 out[t, h] = o
         return out.reshape(T, heads * value_dim).to(q.dtype)
+
+    # -- a bigram embedding, rotations by computed angles, gates a column, two-matrix experts -----------------------------
+    def embed_bigram(self, table, bigram, step, *, state, mul_prev, mul_cur, buckets, out_dtype=None):
+        ids, pos = step.token_ids.tolist(), step.positions.tolist()
+        req, cu, slots = step.request_of_row.tolist(), step.cu_q.tolist(), step.state_slots.tolist()
+        rows = []
+        for t, tok in enumerate(ids):
+            prev = None
+            if req[t] >= 0 and pos[t] > 0:
+                prev = int(state[slots[req[t]], 0]) if t == cu[req[t]] else ids[t - 1]
+            rows.append(buckets if prev is None else (prev * mul_prev + tok * mul_cur) % buckets)
+        for r in range(len(slots)):
+            if slots[r] >= 0 and cu[r + 1] > cu[r]:
+                state[slots[r], 0] = ids[cu[r + 1] - 1]
+        out = table[step.token_ids.long()].float() + bigram[torch.tensor(rows)].float()
+        return out.to(out_dtype or table.dtype)
+
+    def rmsnorm_rows(self, x, weight, eps):
+        v = x.float()
+        return (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight).to(x.dtype)
+
+    def rotate_heads(self, x, *, offset, frequencies, interleaved, positions):
+        out = x.float().clone()
+        rot = 2 * frequencies.shape[0]
+        out[..., offset:offset + rot] = self._turn(out[..., offset:offset + rot].clone(), positions, frequencies, interleaved)
+        return out.to(x.dtype).contiguous()
+
+    def gate_mul(self, a, gate, kind="sigmoid"):
+        g = gate.float()
+        return (a.float() * (torch.sigmoid(g) if kind == "sigmoid" else g * torch.sigmoid(g))).to(a.dtype)
+
+    def activation(self, z, kind):
+        assert kind == "relu2"
+        return (torch.relu(z.float()) ** 2).to(z.dtype)
+
+    def scale_(self, x, scale):
+        return x.mul_(scale)
