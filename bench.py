@@ -358,6 +358,40 @@ def _pegopel_config(width: int, layers: int, kinds=("attention", "attention_2"),
     return out
 
 
+def _sagelorn_config(width: int, layers: int, kinds=("attention", "latent_attention", "attention", "retention"),
+                     mlps=("dense", "moe"), window: int = 1024, share: bool = True, vocab: int = 32768):
+    """Layer sizes that resemble a real model's at this width: 128-wide heads with half as many key/value heads, a
+    rotation over half of each head with stretched slow pairs and windows of ``window`` keys on the attention (every
+    second attention layer reads the keys and values of the one before it, with ``share``); a latent of a quarter of
+    the width with 64 rotated numbers, queries through a latent of half the width; 128-wide retention heads; a dense
+    feed-forward of three times the width, and sixteen two-matrix experts of which two are chosen with a shared expert,
+    with as many active feed-forward weights as the dense one (two matrices of 3/2 width against three)."""
+    heads = width // 128 * 2
+    rot = {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}
+    mixers = {"attention": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "rot": rot,
+                            "scale": 128 ** -0.5, "mask": {"size": window}},
+              "latent_attention": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": width // 4,
+                                   "q_rank": width // 2, "rot": {"dims": 64, "base": 1e4}, "scale": 192 ** -0.5,
+                                   "mask": {"size": window}},
+              "retention": {"heads": heads // 2, "dim": 128, "vdim": 128,
+                            "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, heads // 2 - 1)) for h in range(heads // 2)]}}
+    ffs = {"dense": {"kind": "dense", "ff": 3 * width}, None: None,
+           "moe": {"kind": "moe", "router": {"experts": 16, "top": 2}, "expert": {"ff": 2 * width},
+                   "shared": {"ff": width // 2}}}
+    out, last_owner = [], None
+    for i in range(layers):
+        kind = kinds[i % len(kinds)]
+        mixer = dict(mixers[kind])
+        if kind == "attention":
+            if share and last_owner is not None:
+                mixer["kv_from"], last_owner = last_owner, None
+            else:
+                last_owner = i
+        out.append({"type": kind, "mixer": mixer, "mlp": ffs[mlps[i % len(mlps)] if mlps else None]})
+    return {"architecture": "Sagelorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "logit_scale": 0.5,
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": out}
+
+
 def _dense_config(width: int, layers: int, vocab: int = 32768):
     return dict(QWEN3_0_6B, hidden_size=width, intermediate_size=3 * width, num_hidden_layers=layers,
                 num_attention_heads=width // 128 * 2, num_key_value_heads=width // 128, head_dim=128, vocab_size=vocab,
@@ -429,7 +463,24 @@ def design_run(args) -> int:
     batch, context, prompt, steps = args.batch, CONTEXT, PREFILL_TOKENS, max(8, args.steps // 4)
     with ClockSampler() as clocks:
         for width in (1024, 2048):
-            if args.design == "pegopel":
+            if args.design == "sagelorn":
+                # the design beside the model nearest to it (norms on the outputs, retention, shared caches, routed experts
+                # with a shared one) and the dense decoder; and each of its kinds of layer alone beside its like
+                cases = [("sagelorn", _sagelorn_config(width, 8)), ("tuganex", _tuganex_config(width, 8, share_from=6)),
+                         ("dense", _dense_config(width, 8))]
+                if width == 1024:
+                    cases += [(f"sagelorn {k} x4, no feed-forward", _sagelorn_config(width, 4, kinds=(k,), mlps=None, share=False))
+                              for k in ("attention", "latent_attention", "retention")]
+                    cases += [("sagelorn attention x4, every second reads the one before", _sagelorn_config(width, 4, kinds=("attention",), mlps=None)),
+                              ("pegopel attention_2 x4, no feed-forward, one stream",
+                               _pegopel_config(width, 4, kinds=("attention_2",), mlp=False, streams=0)),
+                              ("rigotar latent_attention x4, no feed-forward", _rigotar_config(width, 4, kinds=("latent_attention",), moe=False)),
+                              ("tuganex retention x4, no feed-forward", _tuganex_config(width, 4, kinds=("retention",), mlps=None)),
+                              ("sagelorn retention x4 with experts", _sagelorn_config(width, 4, kinds=("retention",), mlps=("moe",))),
+                              ("tuganex retention x4 with experts", _tuganex_config(width, 4, kinds=("retention",), mlps=("moe",))),
+                              ("sagelorn retention x4, dense feed-forward", _sagelorn_config(width, 4, kinds=("retention",), mlps=("dense",))),
+                              ("tuganex retention x4, dense feed-forward", _tuganex_config(width, 4, kinds=("retention",), mlps=("dense",)))]
+            elif args.design == "pegopel":
                 # the design beside the models nearest to it (softmax attention over pages and a gated dense
                 # feed-forward), and each of its mixers alone, seeing every key, beside the other attentions alone
                 cases = [("pegopel", _pegopel_config(width, 8)), ("pegopel, every key seen", _pegopel_config(width, 8, window=8192)),
@@ -498,7 +549,7 @@ def main() -> int:
     ap.add_argument("--skip-e2e", action="store_true")
     ap.add_argument("--skip-points", action="store_true")
     ap.add_argument("--skip-prefill", action="store_true")
-    ap.add_argument("--design", default=None, choices=["rigotar", "tuganex", "pegopel"],
+    ap.add_argument("--design", default=None, choices=["rigotar", "tuganex", "pegopel", "sagelorn"],
                     help="instead of the recorded workload: this design's prompt and decode throughput beside the dense decoder's")
     ap.add_argument("--plain-launches", action="store_true",
                     help="launch kernels fully serialised instead of with programmatic dependent launch")

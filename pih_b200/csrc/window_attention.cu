@@ -132,7 +132,7 @@ window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict_
   const float* w = part == 0 ? q_norm : k_norm;
   T* dst = part == 0 ? q_out + row * nq : (slot >= 0 ? cache + slot * width : nullptr);
   if (dst == nullptr) return;
-  const bool pieces = aligned && dim % V == 0 && (!turns || (interleaved && rot % V == 0)) &&
+  const bool pieces = aligned && dim % V == 0 && (!turns || (interleaved ? rot % V == 0 : half % V == 0)) &&
                       n <= static_cast<int>(blockDim.x) * V * kHeld;
   if (pieces) {
     float held[kHeld][V];
@@ -161,7 +161,7 @@ window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict_
 #pragma unroll
       for (int i = 0; i < V; ++i) o[i] = w != nullptr ? held[u][i] * inv * w[e + i] : held[u][i];
       const int c = e % dim;                                   // the piece lies inside a head, and inside or outside the rotation
-      if (turns && c < rot) {
+      if (turns && c < rot && interleaved) {
 #pragma unroll
         for (int i = 0; i < V; i += 2) {
           float cosine, sine;                                     // pair (c + i) / 2
@@ -170,6 +170,22 @@ window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict_
           const float a = o[i], b = o[i + 1];
           o[i] = a * cosine - b * sine;
           o[i + 1] = b * cosine + a * sine;
+        }
+      } else if (turns && c < rot) {
+        // pairs of halves: the partners of this piece are the piece half a rotation away, in the same head
+        const bool first = c < half;
+        const int pe = first ? e + half : e - half;
+        const int pair0 = first ? c : c - half;
+        uint32_t raw[kWords];
+        load_words<kWords>(raw, xp + pe);
+#pragma unroll
+        for (int i = 0; i < V; ++i) {
+          float p = element_of_words<T, kWords>(raw, i);
+          if (w != nullptr) p = p * inv * w[pe + i];
+          float cosine, sine;
+          if (cs != nullptr) { cosine = cs[2 * (pair0 + i)]; sine = cs[2 * (pair0 + i) + 1]; }
+          else sincosf(place * freq[pair0 + i], &sine, &cosine);
+          o[i] = first ? o[i] * cosine - p * sine : o[i] * cosine + p * sine;
         }
       }
       T out[V];

@@ -25,7 +25,9 @@ def silu(z):
 def embed(config, w, tokens, previous):
     """Rows of the token table plus rows of the bigram table, picked by a hash of the pair (token before, token);
     ``previous`` None (nothing came before): the row behind the hashed ones."""
-    b = config["embedding"]["bigram"]
+    b = (config.get("embedding") or {}).get("bigram")
+    if b is None:
+        return w["embed"][torch.tensor(tokens)]
     rows = []
     for t in tokens:
         r = b["buckets"] if previous is None else (previous * b["mul_prev"] + t * b["mul_cur"]) % b["buckets"]
@@ -92,7 +94,7 @@ def attention(h, m, w, pre, eps, keys, values, start):
     out = torch.zeros(T, H, dv, dtype=F)
     for t in range(T):
         p = start + t
-        lo = max(0, p - m["mask"]["size"] + 1)
+        lo = max(0, p - m["mask"]["size"] + 1) if m.get("mask") else 0
         for hd in range(H):
             g = hd // (H // G)
             s = (keys[lo:p + 1, g] @ q[t, hd]) * m["scale"]
@@ -124,7 +126,7 @@ def latent_attention(h, m, w, pre, eps, latents, rotated_keys, start):
     out = torch.zeros(T, H, dv, dtype=F)
     for t in range(T):
         p = start + t
-        lo = max(0, p - m["mask"]["size"] + 1)
+        lo = max(0, p - m["mask"]["size"] + 1) if m.get("mask") else 0
         for hd in range(H):
             s = (k_plain[lo:p + 1, hd] @ q_plain[t, hd] + rotated_keys[lo:p + 1] @ q_rot[t, hd]) * m["scale"]
             out[t, hd] = torch.softmax(s, dim=0) @ v[lo:p + 1, hd]
@@ -221,5 +223,5 @@ def model_layers(config, w, tokens, state=None):
         streams.append(x)
     state["n"] = start + len(tokens)
     state["previous"] = tokens[-1]
-    logits = (rms_unit(x, eps) * (1.0 + w["final.norm"])) @ w["head"].T * config["logit_scale"]
+    logits = (rms_unit(x, eps) * (1.0 + w["final.norm"])) @ w["head"].T * config.get("logit_scale", 1.0)
     return torch.stack(streams), logits, state
