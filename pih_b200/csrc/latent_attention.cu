@@ -22,13 +22,26 @@ template <typename T>
 __global__ void __launch_bounds__(128)
 latent_write_kernel(const T* __restrict__ raw, long long ld, const float* __restrict__ weight, float eps,
                     T* __restrict__ cache, const int* __restrict__ slot_mapping, int rows, int rank, long long cache_rows,
-                    int rot, int interleaved, const float* __restrict__ freq, const int* __restrict__ positions,
-                    uint32_t* err) {
+                    int cache_width, int rot, int interleaved, const float* __restrict__ freq,
+                    const int* __restrict__ positions, const T* __restrict__ q_raw, long long ldq,
+                    const float* __restrict__ q_weight, T* __restrict__ q_out, int q_rank, uint32_t* err) {
   wait_for_prior_kernels();
   launch_dependents();
-  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= rows) return;
+  int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
+  if (row >= rows) {
+    // the warps behind the rows' own: the queries' latent of row ``row - rows``, normed into a buffer of its own
+    row -= rows;
+    if (q_raw == nullptr || row >= rows) return;
+    const T* src = q_raw + static_cast<long long>(row) * ldq;
+    float ss = 0.0f;
+    for (int i = lane; i < q_rank; i += 32) { const float a = to_float<T>(src[i]); ss = fmaf(a, a, ss); }
+    ss = warp_sum(ss);
+    const float scale = 1.0f / sqrtf(ss / static_cast<float>(q_rank) + eps);
+    T* dst = q_out + static_cast<long long>(row) * q_rank;
+    for (int i = lane; i < q_rank; i += 32) dst[i] = from_float<T>(to_float<T>(src[i]) * scale * q_weight[i]);
+    return;
+  }
   const int slot = slot_mapping[row];
   if (slot == kPaddingSlot) return;
   if (slot < 0 || slot >= cache_rows) {
@@ -40,7 +53,7 @@ latent_write_kernel(const T* __restrict__ raw, long long ld, const float* __rest
   for (int i = lane; i < rank; i += 32) { const float a = to_float<T>(src[i]); ss = fmaf(a, a, ss); }
   ss = warp_sum(ss);
   const float scale = 1.0f / sqrtf(ss / static_cast<float>(rank) + eps);
-  T* dst = cache + static_cast<long long>(slot) * (rank + rot);
+  T* dst = cache + static_cast<long long>(slot) * cache_width;      // (columns behind rank + rot are left as they are)
   for (int i = lane; i < rank; i += 32) dst[i] = from_float<T>(to_float<T>(src[i]) * scale * weight[i]);
   if (rot > 0) {
     // behind the latent: ``rot`` more numbers, not normed, rotated by the row's position (32-bit angles)
@@ -59,7 +72,7 @@ latent_write_kernel(const T* __restrict__ raw, long long ld, const float* __rest
   }
 }
 
-constexpr int kLatentPerLane = 16;          // rank <= 32 * 16
+constexpr int kLatentPerLane = 32;          // rank <= 32 * 32 (instances: 2, 4, 8, 16, 24, 32)
 
 // q: [rows, heads, rank] (the folded queries); gate: [rows, ldg] logits, column h, or null; sink: fp32 [heads] or null.
 template <typename T, int kPerLane>
@@ -496,19 +509,26 @@ using namespace pih;
 typedef __nv_bfloat16 bf16;
 
 // raw [rows, ld]: ``rank`` numbers that are normed and, behind them, ``rot`` numbers that are rotated by
-// positions[row] * freq[pair] (pairs of neighbours with ``interleaved``, else halves); cache [slots, rank + rot].
+// positions[row] * freq[pair] (pairs of neighbours with ``interleaved``, else halves); cache [slots, cache_width] with
+// cache_width >= rank + rot (columns of padding behind them are not written).  With q_raw [rows, ldq] the same launch
+// norms its first q_rank columns with q_weight (fp32) and the same eps into q_out [rows, q_rank]: the queries' latent.
 extern "C" int pih_latent_write(int dtype, const void* raw, long long ld, const void* weight, float eps, void* cache,
-                                const void* slot_mapping, int rows, int rank, int page_size, int num_pages, int rot,
-                                int interleaved, const void* freq, const void* positions, void* err, void* stream) {
+                                const void* slot_mapping, int rows, int rank, int page_size, int num_pages,
+                                int cache_width, int rot, int interleaved, const void* freq, const void* positions,
+                                const void* q_raw, long long ldq, const void* q_weight, void* q_out, int q_rank,
+                                void* err, void* stream) {
   if (rows <= 0) return 0;
-  if (rot < 0 || (rot & 1) || (rot > 0 && (freq == nullptr || positions == nullptr))) return PIH_ERR_BAD_ARGUMENT;
+  if (rot < 0 || (rot & 1) || (rot > 0 && (freq == nullptr || positions == nullptr)) || cache_width < rank + rot)
+    return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const long long cache_rows = static_cast<long long>(page_size) * num_pages;
 #define PIH_LW(T)                                                                                                      \
-  launch_kernel(latent_write_kernel<T>, dim3((rows + 3) / 4), dim3(128), 0, s, static_cast<const T*>(raw), ld,         \
+  launch_kernel(latent_write_kernel<T>, dim3(((q_raw != nullptr ? 2 * rows : rows) + 3) / 4), dim3(128), 0, s,         \
+                static_cast<const T*>(raw), ld,                                                                        \
                 static_cast<const float*>(weight), eps, static_cast<T*>(cache), static_cast<const int*>(slot_mapping), \
-                rows, rank, cache_rows, rot, interleaved, static_cast<const float*>(freq),                             \
-                static_cast<const int*>(positions), static_cast<uint32_t*>(err))
+                rows, rank, cache_rows, cache_width, rot, interleaved, static_cast<const float*>(freq),                \
+                static_cast<const int*>(positions), static_cast<const T*>(q_raw), ldq,                                 \
+                static_cast<const float*>(q_weight), static_cast<T*>(q_out), q_rank, static_cast<uint32_t*>(err))
   if (dtype == PIH_F32) PIH_LW(float);
   else if (dtype == PIH_BF16) PIH_LW(bf16);
   else return PIH_ERR_BAD_ARGUMENT;
@@ -538,7 +558,9 @@ extern "C" int pih_latent_attention_generic(int dtype, const void* q, const void
     if (rank <= 64) PIH_LA1(T, 2);                                                                                     \
     else if (rank <= 128) PIH_LA1(T, 4);                                                                               \
     else if (rank <= 256) PIH_LA1(T, 8);                                                                               \
-    else PIH_LA1(T, 16);                                                                                               \
+    else if (rank <= 512) PIH_LA1(T, 16);                                                                              \
+    else if (rank <= 768) PIH_LA1(T, 24);                                                                              \
+    else PIH_LA1(T, 32);                                                                                               \
   } while (0)
   if (dtype == PIH_F32) PIH_LA(float);
   else if (dtype == PIH_BF16) PIH_LA(bf16);
@@ -586,7 +608,9 @@ extern "C" int pih_latent_attention_split(int dtype, const void* q, const void* 
     if (rank <= 64) PIH_LS1(T, 2);                                                                                     \
     else if (rank <= 128) PIH_LS1(T, 4);                                                                               \
     else if (rank <= 256) PIH_LS1(T, 8);                                                                               \
-    else PIH_LS1(T, 16);                                                                                               \
+    else if (rank <= 512) PIH_LS1(T, 16);                                                                              \
+    else if (rank <= 768) PIH_LS1(T, 24);                                                                              \
+    else PIH_LS1(T, 32);                                                                                               \
     PIH_LAUNCH_CHECK();                                                                                                \
     launch_kernel(latent_merge_kernel<T>, dim3(static_cast<unsigned>(items)), dim3(rank >= 256 ? 256 : (rank + 31) / 32 * 32), 0, s, \
                   static_cast<const float*>(partial), static_cast<const T*>(gate), ldg, static_cast<const float*>(sink), \

@@ -81,57 +81,134 @@ rmsnorm_rows_kernel(const T* __restrict__ x, long long ld, const float* __restri
   for (int c = threadIdx.x; c < n; c += blockDim.x) o[c] = from_float<T>(to_float<T>(xr[c]) * inv * weight[c]);
 }
 
-// x [rows, ld]: heads x width columns; out [rows, heads, width] contiguous.
-template <typename T>
-__global__ void rotate_heads_kernel(const T* __restrict__ x, long long ld, T* __restrict__ out, const float* __restrict__ freq,
-                                    const int* __restrict__ positions, long long rows, int heads, int width, int offset,
-                                    int rot, int interleaved) {
-  wait_for_prior_kernels();
-  launch_dependents();
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const long long per_row = static_cast<long long>(heads) * width;
-  if (i >= rows * per_row) return;
-  const long long row = i / per_row;
-  const int e = static_cast<int>(i % per_row);
-  const int c = e % width - offset;                               // column within the rotated part
-  const T* xr = x + row * ld;
-  float v = to_float<T>(xr[e]);
-  if (c >= 0 && c < rot) {
-    const int half = rot >> 1;
-    int pair, other;
-    bool first;
-    if (interleaved) { pair = c >> 1; first = (c & 1) == 0; other = first ? e + 1 : e - 1; }
-    else { pair = c < half ? c : c - half; first = c < half; other = first ? e + half : e - half; }
-    float sn, cs;
-    sincosf(static_cast<float>(positions[row]) * freq[pair], &sn, &cs);
-    const float p = to_float<T>(xr[other]);
-    v = first ? v * cs - p * sn : v * cs + p * sn;
-  }
-  out[i] = from_float<T>(v);
+// 16 bytes as V numbers of T, and back
+template <typename T, int V>
+__device__ __forceinline__ void load_piece(float (&v)[V], const T* src) {
+  __align__(16) T raw[V];
+  *reinterpret_cast<uint4*>(raw) = *reinterpret_cast<const uint4*>(src);
+#pragma unroll
+  for (int i = 0; i < V; ++i) v[i] = to_float<T>(raw[i]);
+}
+template <typename T, int V>
+__device__ __forceinline__ void store_piece(T* dst, const float (&v)[V]) {
+  __align__(16) T raw[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) raw[i] = from_float<T>(v[i]);
+  *reinterpret_cast<uint4*>(dst) = *reinterpret_cast<const uint4*>(raw);
 }
 
-// kind 1: sigmoid(g); 2: silu(g)
-template <typename T>
-__global__ void gate_mul_kernel(const T* __restrict__ a, const T* __restrict__ gate, long long ldg, T* __restrict__ out,
-                                long long rows, int width, int kind) {
+// x [rows, ld]: heads x width columns; out [rows, heads, width] contiguous.  A block is a row: the cosines and sines
+// of the row's rot / 2 angles are formed once, in shared memory (rot <= 2 * kMaxPairs), and serve every head.
+// kPieces: a thread moves 16-byte pieces (width, offset, rot / 2 — or rot with neighbouring pairs — and ld multiples
+// of a piece).
+constexpr int kMaxPairs = 256;
+template <typename T, bool kPieces>
+__global__ void __launch_bounds__(256)
+rotate_heads_kernel(const T* __restrict__ x, long long ld, T* __restrict__ out, const float* __restrict__ freq,
+                    const int* __restrict__ positions, int heads, int width, int offset, int rot, int interleaved) {
+  constexpr int V = 16 / static_cast<int>(sizeof(T));
+  __shared__ float cos_s[kMaxPairs], sin_s[kMaxPairs];
   wait_for_prior_kernels();
   launch_dependents();
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long row = blockIdx.x;
+  const int half = rot >> 1;
+  const float place = static_cast<float>(positions[row]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(place * freq[i], &sin_s[i], &cos_s[i]);
+  __syncthreads();
+  const T* xr = x + row * ld;
+  T* o = out + row * heads * width;
+  const int n = heads * width;
+  if constexpr (kPieces) {
+    for (int e = threadIdx.x * V; e < n; e += blockDim.x * V) {
+      const int c = e % width - offset;
+      float v[V];
+      load_piece<T, V>(v, xr + e);
+      if (c >= 0 && c < rot) {
+        if (interleaved) {
+#pragma unroll
+          for (int i = 0; i < V; i += 2) {
+            const float cs = cos_s[(c + i) >> 1], sn = sin_s[(c + i) >> 1];
+            const float a = v[i], b = v[i + 1];
+            v[i] = a * cs - b * sn;
+            v[i + 1] = b * cs + a * sn;
+          }
+        } else {
+          const bool first = c < half;
+          float p[V];
+          load_piece<T, V>(p, xr + (first ? e + half : e - half));
+          const int pair0 = first ? c : c - half;
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const float cs = cos_s[pair0 + i], sn = sin_s[pair0 + i];
+            v[i] = first ? v[i] * cs - p[i] * sn : v[i] * cs + p[i] * sn;
+          }
+        }
+      }
+      store_piece<T, V>(o + e, v);
+    }
+  } else {
+    for (int e = threadIdx.x; e < n; e += blockDim.x) {
+      const int c = e % width - offset;                           // column within the rotated part
+      float v = to_float<T>(xr[e]);
+      if (c >= 0 && c < rot) {
+        int pair, other;
+        bool first;
+        if (interleaved) { pair = c >> 1; first = (c & 1) == 0; other = first ? e + 1 : e - 1; }
+        else { pair = c < half ? c : c - half; first = c < half; other = first ? e + half : e - half; }
+        const float p = to_float<T>(xr[other]);
+        v = first ? v * cos_s[pair] - p * sin_s[pair] : v * cos_s[pair] + p * sin_s[pair];
+      }
+      o[e] = from_float<T>(v);
+    }
+  }
+}
+
+// kind 1: sigmoid(g); 2: silu(g).  kPieces: 16 bytes a thread (width and ldg multiples of a piece).
+template <typename T, bool kPieces>
+__global__ void gate_mul_kernel(const T* __restrict__ a, const T* __restrict__ gate, long long ldg, T* __restrict__ out,
+                                long long rows, int width, int kind) {
+  constexpr int V = kPieces ? 16 / static_cast<int>(sizeof(T)) : 1;
+  wait_for_prior_kernels();
+  launch_dependents();
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
   if (i >= rows * width) return;
-  const float g = to_float<T>(gate[(i / width) * ldg + i % width]);
+  const long long gi = (i / width) * ldg + i % width;
+  if (kPieces) {
+    float av[V], gv[V];
+    load_piece<T, V>(av, a + i);
+    load_piece<T, V>(gv, gate + gi);
+#pragma unroll
+    for (int j = 0; j < V; ++j) {
+      const float s = 1.0f / (1.0f + expf(-gv[j]));
+      av[j] *= kind == 2 ? gv[j] * s : s;
+    }
+    store_piece<T, V>(out + i, av);
+    return;
+  }
+  const float g = to_float<T>(gate[gi]);
   const float s = 1.0f / (1.0f + expf(-g));
   out[i] = from_float<T>(to_float<T>(a[i]) * (kind == 2 ? g * s : s));
 }
 
-// kind 1: the square of max(z, 0)
-template <typename T>
+// kind 1: the square of max(z, 0).  kPieces: 16 bytes a thread (width and ld multiples of a piece).
+template <typename T, bool kPieces>
 __global__ void unary_act_kernel(const T* __restrict__ z, long long ld, T* __restrict__ out, long long rows, int width,
                                  int kind) {
+  constexpr int V = kPieces ? 16 / static_cast<int>(sizeof(T)) : 1;
   wait_for_prior_kernels();
   launch_dependents();
-  const long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+  const long long i = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) * V;
   if (i >= rows * width) return;
-  const float v = fmaxf(to_float<T>(z[(i / width) * ld + i % width]), 0.0f);
+  const long long zi = (i / width) * ld + i % width;
+  if (kPieces) {
+    float v[V];
+    load_piece<T, V>(v, z + zi);
+#pragma unroll
+    for (int j = 0; j < V; ++j) { v[j] = fmaxf(v[j], 0.0f); v[j] *= v[j]; }
+    store_piece<T, V>(out + i, v);
+    return;
+  }
+  const float v = fmaxf(to_float<T>(z[zi]), 0.0f);
   out[i] = from_float<T>(v * v);
 }
 
@@ -193,23 +270,26 @@ extern "C" int pih_rmsnorm_rows(int dtype, const void* x, long long ld, const vo
   return 0;
 }
 
+static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
 // x [rows, ld] holding heads x width columns; out [rows, heads, width]; freq fp32 [rot / 2]
 extern "C" int pih_rotate_heads(int dtype, const void* x, long long ld, void* out, const void* freq, const void* positions,
                                 int rows, int heads, int width, int offset, int rot, int interleaved, void* stream) {
   if (rows <= 0 || heads <= 0 || width <= 0) return 0;
   if (rot < 0 || (rot & 1) || offset < 0 || offset + rot > width) return PIH_ERR_BAD_ARGUMENT;
+  if (rot > 2 * kMaxPairs) return PIH_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const long long n = static_cast<long long>(rows) * heads * width;
-  if (dtype == PIH_BF16)
-    launch_kernel(rotate_heads_kernel<bf16>, flat_grid(n), dim3(256), 0, s, static_cast<const bf16*>(x), ld,
-                  static_cast<bf16*>(out), static_cast<const float*>(freq), static_cast<const int*>(positions),
-                  static_cast<long long>(rows), heads, width, offset, rot, interleaved);
-  else if (dtype == PIH_F32)
-    launch_kernel(rotate_heads_kernel<float>, flat_grid(n), dim3(256), 0, s, static_cast<const float*>(x), ld,
-                  static_cast<float*>(out), static_cast<const float*>(freq), static_cast<const int*>(positions),
-                  static_cast<long long>(rows), heads, width, offset, rot, interleaved);
-  else
-    return PIH_ERR_BAD_ARGUMENT;
+  const int V = dtype == PIH_F32 ? 4 : 8;
+  const bool pieces = width % V == 0 && offset % V == 0 && ld % V == 0 && (interleaved ? rot % V == 0 : (rot / 2) % V == 0) &&
+                      aligned16(x) && aligned16(out);
+  const dim3 block(heads * width >= 2048 ? 256 : 128);
+#define PIH_RH(T, P)                                                                                                   \
+  launch_kernel(rotate_heads_kernel<T, P>, dim3(rows), block, 0, s, static_cast<const T*>(x), ld, static_cast<T*>(out), \
+                static_cast<const float*>(freq), static_cast<const int*>(positions), heads, width, offset, rot, interleaved)
+  if (dtype == PIH_BF16) { if (pieces) PIH_RH(bf16, true); else PIH_RH(bf16, false); }
+  else if (dtype == PIH_F32) { if (pieces) PIH_RH(float, true); else PIH_RH(float, false); }
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_RH
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -220,14 +300,16 @@ extern "C" int pih_gate_mul(int dtype, const void* a, const void* gate, long lon
   if (rows <= 0 || width <= 0) return 0;
   if (kind != 1 && kind != 2) return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == PIH_BF16)
-    launch_kernel(gate_mul_kernel<bf16>, flat_grid(rows * width), dim3(256), 0, s, static_cast<const bf16*>(a),
-                  static_cast<const bf16*>(gate), ldg, static_cast<bf16*>(out), rows, width, kind);
-  else if (dtype == PIH_F32)
-    launch_kernel(gate_mul_kernel<float>, flat_grid(rows * width), dim3(256), 0, s, static_cast<const float*>(a),
-                  static_cast<const float*>(gate), ldg, static_cast<float*>(out), rows, width, kind);
-  else
-    return PIH_ERR_BAD_ARGUMENT;
+  const int V = dtype == PIH_F32 ? 4 : 8;
+  const bool pieces = width % V == 0 && ldg % V == 0 && aligned16(a) && aligned16(gate) && aligned16(out);
+  const long long n = rows * width / (pieces ? V : 1);
+#define PIH_GM(T, P)                                                                                                   \
+  launch_kernel(gate_mul_kernel<T, P>, flat_grid(n), dim3(256), 0, s, static_cast<const T*>(a),                        \
+                static_cast<const T*>(gate), ldg, static_cast<T*>(out), rows, width, kind)
+  if (dtype == PIH_BF16) { if (pieces) PIH_GM(bf16, true); else PIH_GM(bf16, false); }
+  else if (dtype == PIH_F32) { if (pieces) PIH_GM(float, true); else PIH_GM(float, false); }
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_GM
   PIH_LAUNCH_CHECK();
   return 0;
 }
@@ -238,14 +320,16 @@ extern "C" int pih_unary_act(int dtype, const void* z, long long ld, void* out, 
   if (rows <= 0 || width <= 0) return 0;
   if (kind != 1) return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (dtype == PIH_BF16)
-    launch_kernel(unary_act_kernel<bf16>, flat_grid(rows * width), dim3(256), 0, s, static_cast<const bf16*>(z), ld,
-                  static_cast<bf16*>(out), rows, width, kind);
-  else if (dtype == PIH_F32)
-    launch_kernel(unary_act_kernel<float>, flat_grid(rows * width), dim3(256), 0, s, static_cast<const float*>(z), ld,
-                  static_cast<float*>(out), rows, width, kind);
-  else
-    return PIH_ERR_BAD_ARGUMENT;
+  const int V = dtype == PIH_F32 ? 4 : 8;
+  const bool pieces = width % V == 0 && ld % V == 0 && aligned16(z) && aligned16(out);
+  const long long n = rows * width / (pieces ? V : 1);
+#define PIH_UA(T, P)                                                                                                   \
+  launch_kernel(unary_act_kernel<T, P>, flat_grid(n), dim3(256), 0, s, static_cast<const T*>(z), ld,                   \
+                static_cast<T*>(out), rows, width, kind)
+  if (dtype == PIH_BF16) { if (pieces) PIH_UA(bf16, true); else PIH_UA(bf16, false); }
+  else if (dtype == PIH_F32) { if (pieces) PIH_UA(float, true); else PIH_UA(float, false); }
+  else return PIH_ERR_BAD_ARGUMENT;
+#undef PIH_UA
   PIH_LAUNCH_CHECK();
   return 0;
 }

@@ -92,7 +92,9 @@ window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict_
   constexpr int V = 16 / static_cast<int>(sizeof(T));         // elements a piece
   constexpr int kWords = 4;
   constexpr int kHeld = 2;                                     // pieces a thread keeps
+  constexpr int kTurnPairs = 128;                              // computed angles: their cosines and sines, once a block
   __shared__ float scratch[33];
+  __shared__ float turn_s[2 * kTurnPairs];
   wait_for_prior_kernels();
   launch_dependents();
   const long long row = blockIdx.x;
@@ -132,6 +134,12 @@ window_qk_prepare_kernel(const T* __restrict__ src, long long ld, T* __restrict_
   const float* w = part == 0 ? q_norm : k_norm;
   T* dst = part == 0 ? q_out + row * nq : (slot >= 0 ? cache + slot * width : nullptr);
   if (dst == nullptr) return;
+  if (turns && cs == nullptr && half <= kTurnPairs) {
+    // the row's angles serve every head: their cosines and sines are formed once and read like a table's row
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(place * freq[i], &turn_s[2 * i + 1], &turn_s[2 * i]);
+    __syncthreads();
+    cs = turn_s;
+  }
   const bool pieces = aligned && dim % V == 0 && (!turns || (interleaved ? rot % V == 0 : half % V == 0)) &&
                       n <= static_cast<int>(blockDim.x) * V * kHeld;
   if (pieces) {

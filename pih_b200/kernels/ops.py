@@ -732,21 +732,31 @@ class CudaOps:
 
     def latent_write(self, raw: torch.Tensor, weight: torch.Tensor, eps: float, cache: torch.Tensor,
                      slot_mapping: torch.Tensor, frequencies: Optional[torch.Tensor] = None, interleaved: bool = False,
-                     positions: Optional[torch.Tensor] = None) -> None:
+                     positions: Optional[torch.Tensor] = None, query_latent: Optional[torch.Tensor] = None,
+                     query_weight: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
         """``rmsnorm(raw) * weight`` of every row into its slot of the paged latent cache ``[pages, page_size, rank]``.
         With ``frequencies`` (fp32 ``[rot / 2]``) the rows hold ``rot`` more numbers behind the ``rank`` normed ones:
         they are not normed but rotated by ``positions[row] * f_i`` (pairs of neighbours with ``interleaved``, else
-        halves) and cached behind the latent (the cache is ``rank + rot`` wide)."""
+        halves) and cached behind the latent.  The cache may be wider than ``rank + rot`` (columns of padding, which
+        stay as they are: zero).  ``query_latent`` ``[T, n]`` (a view) with ``query_weight`` (fp32 ``[n]``): the same
+        launch norms it too (the same ``eps``) and returns it as ``[T, n]`` contiguous."""
         T, width = raw.shape
         rot = 2 * frequencies.shape[0] if frequencies is not None else 0
         rank = width - rot
         num_pages, page_size = cache.shape[0], cache.shape[1]
-        assert raw.stride(1) == 1 and cache.dtype == raw.dtype and cache.shape[2] == width and weight.shape[0] == rank
+        assert raw.stride(1) == 1 and cache.dtype == raw.dtype and cache.shape[2] >= width and weight.shape[0] == rank
+        q_out, q_rank, ldq = None, 0, 0
+        if query_latent is not None:
+            q_rank, ldq = query_latent.shape[1], query_latent.stride(0)
+            assert query_latent.shape[0] == T and query_latent.stride(1) == 1 and query_latent.dtype == raw.dtype
+            assert query_weight.dtype == torch.float32 and query_weight.shape[0] == q_rank
+            q_out = torch.empty(T, q_rank, dtype=raw.dtype, device=raw.device)
         rc = self.lib.pih_latent_write(_DT[raw.dtype], _ptr(raw), c_ll(raw.stride(0)), _ptr(weight), c_float(eps),
-                                       _ptr(cache), _ptr(slot_mapping), T, rank, page_size, num_pages, rot,
-                                       1 if interleaved else 0, _ptr(frequencies), _ptr(positions), self._err(),
-                                       self._stream())
+                                       _ptr(cache), _ptr(slot_mapping), T, rank, page_size, num_pages, cache.shape[2], rot,
+                                       1 if interleaved else 0, _ptr(frequencies), _ptr(positions), _ptr(query_latent),
+                                       c_ll(ldq), _ptr(query_weight), _ptr(q_out), q_rank, self._err(), self._stream())
         self._check(rc, "latent_write")
+        return q_out
 
     def latent_attention(self, q: torch.Tensor, *, gate: Optional[torch.Tensor], sink: Optional[torch.Tensor],
                          cache: torch.Tensor, block_table: torch.Tensor, step, scale: float, window: int = 0) -> torch.Tensor:

@@ -17,6 +17,10 @@ numbers a token, one rotated key part for all heads.  The cached vector becomes 
 folded query ``[K_h^T q_h | rotated q part]``: their dot product is the sum of both score terms, so the same kernel
 serves (the fold's matrix carries an identity block for the rotated columns, the value fold zeros).  With
 ``query_rank`` the queries come through a latent of their own: ``q = W_uq rmsnorm(W_dq h)``.
+
+In bfloat16 the cached vector is padded with zero columns to the next width that the tensor-core attention kernel has
+an instance for (``TENSOR_CORE_WIDTHS``); the folds' matrices have zeros there, so scores and sums are what they are
+without the padding.
 """
 from __future__ import annotations
 
@@ -24,6 +28,19 @@ import torch
 
 from .registry import PagedVectorNeed, Runtime, TensorInfo, part_class, register_mixer
 from ._bind import bind_matrix
+
+
+TENSOR_CORE_WIDTHS = (64, 128, 192, 256, 384, 512)
+
+
+def cached_width(spec, dtype) -> int:
+    """Numbers cached per token: the latent and the rotated key part, in bfloat16 padded to a tensor-core width."""
+    width = spec.latent_rank + getattr(spec, "rotary_dim", 0)
+    if dtype == torch.bfloat16:
+        for w in TENSOR_CORE_WIDTHS:
+            if width <= w:
+                return w
+    return width
 
 
 @register_mixer("latent_attention")
@@ -71,13 +88,14 @@ class LatentAttention:
             self.q_norm = weights[n["q_down_norm"]].to(**f32).contiguous()
         # q'_h = q_h . K_h with K_h [D, R]: as a product with rows of outputs, the weight is K_h^T [R, D]; the rotated
         # columns of a head's query pass through an identity block, and the value fold has zeros for them
-        fold = torch.zeros(H, R + rot, D + rot, dtype=torch.float32)
+        self.cached = C = cached_width(spec, rt.dtype)
+        fold = torch.zeros(H, C, D + rot, dtype=torch.float32)
         fold[:, :R, :D] = weights[n["up_k"]].to(torch.float32).reshape(H, D, R).transpose(1, 2)
-        fold[:, R:, D:] = torch.eye(rot)
-        self.w_fold_k = bind_matrix(fold, rt)                                                  # [H, R + rot, D + rot]
-        up_v = torch.zeros(H, V, R + rot, dtype=torch.float32)
+        fold[:, R:R + rot, D:] = torch.eye(rot)
+        self.w_fold_k = bind_matrix(fold, rt)                                                  # [H, C, D + rot]
+        up_v = torch.zeros(H, V, C, dtype=torch.float32)
         up_v[:, :, :R] = weights[n["up_v"]].to(torch.float32).reshape(H, V, R)
-        self.w_up_v = bind_matrix(up_v, rt)                                                    # [H, V, R + rot]
+        self.w_up_v = bind_matrix(up_v, rt)                                                    # [H, V, C]
         self.w_o = bind_matrix(weights[n["o"]], rt)
         self.down_norm = weights[n["down_norm"]].to(**f32).contiguous()
         self.sink = weights[n["sink"]].to(**f32).contiguous() if spec.sink else None
@@ -91,7 +109,7 @@ class LatentAttention:
                                 "(a position part that computes its angles)")
 
     def cache_need(self):
-        return PagedVectorNeed(self.spec.latent_rank + self.rot, self.window)
+        return PagedVectorNeed(self.cached, self.window)
 
     def forward(self, x, step, cache):
         s, ops = self.spec, self.rt.ops
@@ -103,14 +121,17 @@ class LatentAttention:
         if rot:
             rotation = dict(frequencies=self.position.frequencies(), interleaved=self.position.interleaved,
                             positions=step.positions)
-        ops.latent_write(proj[:, F:F + R + rot], self.down_norm, s.norm_eps, cache.kv, cache.slot_mapping, **rotation)
         if self.q_rank is None:
+            ops.latent_write(proj[:, F:F + R + rot], self.down_norm, s.norm_eps, cache.kv, cache.slot_mapping, **rotation)
             q = proj[:, :F].view(T, H, D + rot)
         else:
-            q = ops.linear(ops.rmsnorm_rows(proj[:, :F], self.q_norm, s.norm_eps), self.w_q_up).view(T, H, D + rot)
+            # the kernel that norms the latent into the cache norms the queries' latent beside it
+            cq = ops.latent_write(proj[:, F:F + R + rot], self.down_norm, s.norm_eps, cache.kv, cache.slot_mapping,
+                                  query_latent=proj[:, :F], query_weight=self.q_norm, **rotation)
+            q = ops.linear(cq, self.w_q_up).view(T, H, D + rot)
         if rot:
             q = ops.rotate_heads(q, offset=D, **rotation)                   # the last ``rot`` columns of every head
-        q_lat = ops.linear_batched(q, self.w_fold_k)                                            # [T, H, R + rot]
+        q_lat = ops.linear_batched(q, self.w_fold_k)                                            # [T, H, C]
         gate = proj[:, F + R + rot:] if s.gated else None
         o_lat = ops.latent_attention(q_lat, gate=gate if self.gate_per == "head" else None, sink=self.sink,
                                      cache=cache.kv, block_table=cache.block_table, step=step, scale=s.scale,

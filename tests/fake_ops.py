@@ -257,19 +257,24 @@ class FakeOps:
         a, b = x[..., :rot // 2], x[..., rot // 2:]
         return torch.cat([a * c - b * s, b * c + a * s], dim=-1)
 
-    def latent_write(self, raw, weight, eps, cache, slot_mapping, frequencies=None, interleaved=False, positions=None):
+    def latent_write(self, raw, weight, eps, cache, slot_mapping, frequencies=None, interleaved=False, positions=None,
+                     query_latent=None, query_weight=None):
         rot = 2 * frequencies.shape[0] if frequencies is not None else 0
         rank = raw.shape[1] - rot
         v = raw[:, :rank].float()
         c = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight
         if rot:
             c = torch.cat([c, self._turn(raw[:, rank:].float(), positions, frequencies, interleaved)], dim=-1)
+        if cache.shape[-1] > c.shape[1]:                                     # columns of padding stay zero
+            c = torch.cat([c, torch.zeros(c.shape[0], cache.shape[-1] - c.shape[1])], dim=-1)
         flat = cache.view(-1, cache.shape[-1])
         for t, slot in enumerate(slot_mapping.tolist()):
             if slot == -2:
                 continue
             assert slot >= 0
             flat[slot] = c[t].to(cache.dtype)
+        if query_latent is not None:
+            return self.rmsnorm_rows(query_latent, query_weight, eps)
 
     def latent_attention(self, q, *, gate, sink, cache, block_table, step, scale, window=0):
         T, heads, rank = q.shape

@@ -225,3 +225,22 @@ def test_configurations_drawn_at_random_with_stand_in_kernels(tmp_path, seed):
     for rid, ref in sm.plain_logits(d, requests).items():
         assert float((got[rid].double() - ref).abs().max()) < 3e-4 * max(1.0, float(ref.abs().max())), rid
     cache.check()
+
+
+def test_the_cached_latent_is_padded_to_a_tensor_core_width_in_bfloat16(tmp_path):
+    """In bfloat16 the cache of a latent attention layer is as wide as the next tensor-core instance; the columns of
+    padding stay zero and change nothing (here: stand-in kernels that round to bfloat16 after each step)."""
+    from pih_b200.engine.factory import create_runner
+    d = sm.write_model(tmp_path / "m", sm.single_layer("latent_attention"), seed=1, sigma=0.2)
+    requests = traces.make_requests(120, [23, 5], seed=3)
+    steps = traces.portions(requests)
+    _, model, cache, runner = create_runner(d, "bfloat16", device="cpu", page_size=4, max_cache_tokens=32, max_requests=2,
+                                            ops=FakeOps())
+    assert [g.need.width for g in cache.groups] == [64] and model.blocks[0].mixer.w_fold_k.shape == (2, 64, 18)
+    got = traces.replay(runner, steps)
+    assert bool((cache.groups[0].kv[..., 24:] == 0).all()) and bool((cache.groups[0].kv[..., :24] != 0).any())
+    for rid, ref in sm.plain_logits(d, requests).items():
+        err = (got[rid].double() - ref).pow(2).mean().sqrt() / ref.std()
+        assert float(err) < 0.05, (rid, float(err))
+    _, _, cache32, _ = create_runner(d, "float32", device="cpu", page_size=4, max_cache_tokens=32, max_requests=2, ops=FakeOps())
+    assert [g.need.width for g in cache32.groups] == [24]
