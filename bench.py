@@ -362,15 +362,15 @@ def _sagelorn_config(width: int, layers: int, kinds=("attention", "latent_attent
                      mlps=("dense", "moe"), window: int = 1024, share: bool = True, vocab: int = 32768):
     """Layer sizes that resemble a real model's at this width: 128-wide heads with half as many key/value heads, a
     rotation over half of each head with stretched slow pairs and windows of ``window`` keys on the attention (every
-    second attention layer reads the keys and values of the one before it, with ``share``); a latent and 64 rotated
-    numbers that are a quarter of the width together, queries through a latent of half the width; 128-wide retention
-    heads; a dense feed-forward of three times the width, and sixteen two-matrix experts of twice the width of which two
+    second attention layer reads the keys and values of the one before it, with ``share``); latent attention with as
+    many heads as Rigotar's (one a 128 of the width), a latent and 64 rotated numbers that are a quarter of the width
+    together, queries through a latent of half the width; 128-wide retention heads; a dense feed-forward of three times the width, and sixteen two-matrix experts of twice the width of which two
     are chosen, with a shared expert of half the width: as many active feed-forward weights as the dense one."""
     heads = width // 128 * 2
     rot = {"dims": 64, "base": 1e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 2048}}
     mixers = {"attention": {"heads": heads, "kv_heads": max(1, heads // 2), "dim": 128, "vdim": 128, "rot": rot,
                             "scale": 128 ** -0.5, "mask": {"size": window}},
-              "latent_attention": {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": width // 4 - 64,
+              "latent_attention": {"heads": heads // 2, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": width // 4 - 64,
                                    "q_rank": width // 2, "rot": {"dims": 64, "base": 1e4}, "scale": 192 ** -0.5,
                                    "mask": {"size": window}},
               "retention": {"heads": heads // 2, "dim": 128, "vdim": 128,

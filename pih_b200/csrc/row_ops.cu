@@ -113,7 +113,7 @@ rotate_heads_kernel(const T* __restrict__ x, long long ld, T* __restrict__ out, 
   const long long row = blockIdx.x;
   const int half = rot >> 1;
   const float place = static_cast<float>(positions[row]);
-  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(place * freq[i], &sin_s[i], &cos_s[i]);
+  for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(place * freq[i], &sin_s[i], &cos_s[i]);   // (half <= kMaxPairs)
   __syncthreads();
   const T* xr = x + row * ld;
   T* o = out + row * heads * width;

@@ -72,6 +72,17 @@ S2 = {"architecture": "Sagelorn", "vocab": 257, "width": 64, "norm": {"eps": 1e-
            "mlp": _dense(100)},
           {"type": "attention", "mixer": _att(window=64, kv_from=1, **_A2), "mlp": _dense(48)},
       ]}
+# Sizes that no 16-byte path and no tensor-core instance takes: an odd vocabulary, a width and sizes that are multiples
+# of two only, three query heads a key/value head, a window of three keys, all experts but one chosen.
+_A3 = dict(heads=3, kv_heads=1, dim=10, vdim=6, rot=_rot(6, 20.0, (3.0, 1.0, 2.0, 10)), scale=0.4)
+S3 = {"architecture": "Sagelorn", "vocab": 77, "width": 50, "norm": {"eps": 1e-5}, "logit_scale": 2.5,
+      "embedding": {"bigram": {"buckets": 2, "mul_prev": 1, "mul_cur": 1}},
+      "layers": [
+          {"type": "latent_attention", "mixer": _lat(3, 6, 2, 10, 14, 10, _rot(2, 9.0), 0.3, 3), "mlp": _moe(3, 2, 18, shared=6)},
+          {"type": "attention", "mixer": _att(window=5, **_A3), "mlp": _dense(30)},
+          {"type": "retention", "mixer": _ret(1, 6, 10, [0.9]), "mlp": None},
+          {"type": "attention", "mixer": _att(window=40, kv_from=1, **_A3), "mlp": _moe(2, 1, 10)},
+      ]}
 CONFIGS = {"S1": S1, "S2": S2}
 SIGMA = {"S1": 0.12, "S2": 0.15}
 

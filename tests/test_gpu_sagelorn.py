@@ -414,6 +414,23 @@ def test_batches_against_each_request_alone(dirs):
         assert float((torch.cat(got[rid]).cpu() - alone[rid]).abs().max()) < 1e-6, rid
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_sizes_that_only_the_plain_kernels_take(tmp_path, dtype):
+    """A width, head sizes, ranks and a vocabulary that are multiples of two at most: no 16-byte piece, no tensor-core
+    instance, no few-rows product; a mixed schedule against the plain implementation."""
+    from pih_b200.engine.factory import create_runner
+    raw = sm.S3 if dtype == "float32" else sm.all_chosen(sm.S3)
+    d = sm.write_model(tmp_path / "m", raw, seed=11, sigma=0.2)
+    requests = traces.make_requests(77, [50, 21, 1, 2, 34], seed=12)
+    steps = traces.mixed(requests, seed=3, max_live=3)
+    _, model, cache, runner = create_runner(d, dtype, page_size=8, max_cache_tokens=traces.peak_tokens(steps, round_to=8),
+                                            max_requests=3)
+    got = traces.replay(runner, steps)
+    model.rt.ops.check_errors()
+    _check(got, sm.plain_logits(d, requests), dtype, f"odd sizes {dtype}")
+    cache.check()
+
+
 @pytest.mark.parametrize("seed", range(8))
 def test_configurations_drawn_at_random(tmp_path, seed):
     """Sizes, orders of layers, shared caches with windows of their own and constants drawn at random (odd sizes and
