@@ -302,11 +302,12 @@ def _paged_rows(rows, page, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("rank, rot, heads", [(40, 8, 3), (96, 32, 4), (18, 6, 1), (112, 16, 5)])
+@pytest.mark.parametrize("rank, rot, heads", [(40, 8, 3), (96, 32, 4), (18, 6, 1), (112, 16, 5), (520, 56, 2), (800, 32, 1)])
 def test_latent_attention_window_edges_with_a_rotated_key_part(dtype, rank, rot, heads):
     """300 cached vectors [latent | rotated key part] of which ONE matches the folded query (its score stands out by
     construction, half of it through the rotated part): as the oldest key of the window, one place beyond it, across a
-    page border and far back without a window — as a single decoded row and as the last row of a portion of 70 rows."""
+    page border and far back without a window — as a single decoded row and as the last row of a portion of 70 rows.
+    Widths with a tensor-core instance (128), without one, and beyond the widest instance (576, 832: the warp kernels)."""
     ops = _ops()
     n, page, scale, rows, width = 300, 16, 0.4, 70, rank + rot
     last = n - 1
