@@ -87,6 +87,7 @@ struct SkinnyParams {
   long long ldx, ldw, ldo;
   int stages;                                    // of the ring of units
   int activation;                                // of the gated epilogue: 0 SiLU, 1 the tanh form of GELU
+  int unary;                                     // of the plain epilogue: 0 none, 1 the square of max(rounded product, 0)
   uint32_t* error;
 };
 
@@ -344,6 +345,10 @@ __global__ void __launch_bounds__(SK_THREADS, 2) skinny_gemm_kernel(const Skinny
         for (int w = 0; w < SK_WARPS; ++w) sum += all[w * RED + t * 128 + el * 4 + er];
         // (a residual never comes with two 8-row groups of 16 tokens: see the dispatch)
         if (p.residual != nullptr) sum = __bfloat162float(__float2bfloat16_rn(sum)) + res_now;
+        if (p.unary == 1) {                                  // the activation of a two-matrix feed-forward, on the product's rounding
+          sum = fmaxf(__bfloat162float(__float2bfloat16_rn(sum)), 0.0f);
+          sum *= sum;
+        }
         out[etok * p.ldo + col] = from_float<OT>(sum);
       }
     }
@@ -594,7 +599,8 @@ extern "C" int pih_set_skinny_rule(int on) {
 //              written to x_out (a buffer other than x: blocks read x while one of them writes)
 //   norm_w     nullable: RMSNorm (weight dtype norm_dtype, eps) of the rows before the product
 //   swiglu     W rows come in blocks of 16 = 8 gate rows + their 8 up rows; out is [M, N / 2]; 1: SiLU(gate) * up,
-//              2: the tanh form of GELU instead of SiLU
+//              2: the tanh form of GELU instead of SiLU; 3: no gate at all, out [M, N] is the square of
+//              max(round(x . W^T), 0) (not with a residual)
 //   residual   nullable (not with swiglu): out = round(round(x . W^T) + residual), the residual add that follows an
 //              output projection, with its two roundings; rows of ldo elements; may not be `out` itself
 //   error      the device's error word (a bounded wait that ran out is reported there)
@@ -603,7 +609,8 @@ extern "C" int pih_gemm_skinny(const void* x, const void* delta, void* x_out, in
                                float eps, const void* W, void* out, const void* residual, int M, int N, int K,
                                long long ldx, long long ldw, long long ldo, int swiglu, uint32_t* error, void* stream) {
   if (M <= 0 || N <= 0) return 0;
-  if (!skinny_takes(x, W, M, K, ldx, ldw) || (swiglu && (N % 16 || residual != nullptr)) ||
+  if (swiglu < 0 || swiglu > 3) return PIH_ERR_BAD_ARGUMENT;
+  if (!skinny_takes(x, W, M, K, ldx, ldw) || (swiglu && swiglu != 3 && N % 16) || (swiglu && residual != nullptr) ||
       (reinterpret_cast<uintptr_t>(norm_w) & 15) || residual == out || (norm_w != nullptr && K % 8) ||
       (delta != nullptr && ((reinterpret_cast<uintptr_t>(delta) & 15) || x_out == nullptr || x_out == x)))
     return PIH_ERR_UNSUPPORTED;
@@ -632,8 +639,9 @@ extern "C" int pih_gemm_skinny(const void* x, const void* delta, void* x_out, in
   p.M = M, p.N = N, p.K = K;
   p.ldx = ldx, p.ldw = ldw, p.ldo = ldo;
   p.error = error;
-  const bool sw = swiglu != 0;
+  const bool sw = swiglu == 1 || swiglu == 2;
   p.activation = swiglu == 2 ? 1 : 0;
+  p.unary = swiglu == 3 ? 1 : 0;
 #define PIH_SKINNY(MR, NORM, NW) dispatch_skinny<MR, NORM, NW>(sw, p, s)
   if (norm_w == nullptr) return M <= 8 ? PIH_SKINNY(8, false, float) : PIH_SKINNY(16, false, float);
   if (norm_dtype == PIH_F32) return M <= 8 ? PIH_SKINNY(8, true, float) : PIH_SKINNY(16, true, float);

@@ -406,18 +406,43 @@ moe_gemv_kernel(const T* __restrict__ x, long long ldx, int row_div, const int* 
 }
 
 // Few rows, many small matrices (a head's or a diagonal block's): out[t][b][n] = x[t][b] . W[b][n], a warp four output
-// columns, the matrix rows read with 16-byte loads.  K a multiple of 8 (bf16).
+// columns, the matrix rows read with 16-byte loads.  K a multiple of 8 (bf16).  Two optional steps of the mixers that use
+// it for their folds: ``freq`` — the columns rot_offset .. rot_offset + rot of every x[t][b] are rotated by
+// positions[t] * freq[pair] on their way into shared memory (32-bit angles, rounded to T like a rotation's own kernel
+// would leave them; pairs of neighbours with ``interleaved``, else halves); ``gate`` — the output, rounded, is multiplied
+// by sigmoid(gate[t * ldg + b * N + n]).
 template <typename T, typename TC>
 __global__ void __launch_bounds__(256)
 batched_gemv_kernel(const T* __restrict__ x, long long ldx, long long batch_x, const T* __restrict__ W, TC* __restrict__ out,
-                    int batches, int N, int K) {
+                    int batches, int N, int K, const float* __restrict__ freq, const int* __restrict__ positions,
+                    int rot_offset, int rot, int interleaved, const T* __restrict__ gate, long long ldg) {
   constexpr int kVec = 16 / sizeof(T), kCols = 4;
   extern __shared__ float xs[];
   wait_for_prior_kernels();
   launch_dependents();
   const int t = blockIdx.x / batches, b = blockIdx.x % batches;
   const T* xr = x + t * ldx + b * batch_x;
-  for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float<T>(xr[k]);
+  if (freq == nullptr) {
+    for (int k = threadIdx.x; k < K; k += blockDim.x) xs[k] = to_float<T>(xr[k]);
+  } else {
+    const float place = static_cast<float>(positions[t]);
+    const int half = rot >> 1;
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+      float v = to_float<T>(xr[k]);
+      const int c = k - rot_offset;
+      if (c >= 0 && c < rot) {
+        int pair, other;
+        bool first;
+        if (interleaved) { pair = c >> 1; first = (c & 1) == 0; other = first ? k + 1 : k - 1; }
+        else { pair = c < half ? c : c - half; first = c < half; other = first ? k + half : k - half; }
+        float sn, cs;
+        sincosf(place * freq[pair], &sn, &cs);
+        const float p = to_float<T>(xr[other]);
+        v = round_to<T>(first ? v * cs - p * sn : v * cs + p * sn);
+      }
+      xs[k] = v;
+    }
+  }
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n0 = (blockIdx.y * (blockDim.x >> 5) + warp) * kCols;
@@ -441,8 +466,14 @@ batched_gemv_kernel(const T* __restrict__ x, long long ldx, long long batch_x, c
   }
 #pragma unroll
   for (int c = 0; c < kCols; ++c) {
-    const float v = warp_sum(acc[c]);
-    if (lane == 0 && n0 + c < N) out[(static_cast<long long>(blockIdx.x)) * N + n0 + c] = from_float<TC>(v);
+    float v = warp_sum(acc[c]);
+    if (lane == 0 && n0 + c < N) {
+      if (gate != nullptr) {
+        const float g = to_float<T>(gate[t * ldg + static_cast<long long>(b) * N + n0 + c]);
+        v = round_to<TC>(v) * (1.0f / (1.0f + expf(-g)));
+      }
+      out[(static_cast<long long>(blockIdx.x)) * N + n0 + c] = from_float<TC>(v);
+    }
   }
 }
 
@@ -668,19 +699,28 @@ extern "C" int pih_moe_combine_bf16(const void* y, const void* ints, const void*
 }
 
 // out[t][b] = x[t][b] . W[b]^T for few rows t in bf16: x element (t, b, k) at t * ldx + b * batch_x + k, W [batches, N, K],
-// out [rows, batches, N] contiguous, bf16 or fp32.
+// out [rows, batches, N] contiguous, bf16 or fp32.  freq fp32 [rot / 2] with positions int32 [rows]: the columns
+// rot_offset .. rot_offset + rot of every x[t][b] are rotated first.  gate bf16 [rows, ldg] (column b * N + n): the
+// rounded output times its sigmoid.  Both nullable.
 extern "C" int pih_batched_gemv(int out_dtype, const void* x, long long ldx, long long batch_x, const void* W, void* out,
-                                int rows, int batches, int N, int K, void* stream) {
+                                int rows, int batches, int N, int K, const void* freq, const void* positions,
+                                int rot_offset, int rot, int interleaved, const void* gate, long long ldg, void* stream) {
   if (rows <= 0 || batches <= 0 || N <= 0) return 0;
   if (K % 8 || K > 12288 || static_cast<long long>(rows) * batches > 65535 * 16) return PIH_ERR_UNSUPPORTED;
+  if (freq != nullptr && (positions == nullptr || rot < 0 || (rot & 1) || rot_offset < 0 || rot_offset + rot > K))
+    return PIH_ERR_BAD_ARGUMENT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   dim3 grid(rows * batches, (N + 31) / 32);
   if (out_dtype == PIH_BF16)
     launch_kernel(batched_gemv_kernel<bf16, bf16>, grid, dim3(256), K * sizeof(float), s, static_cast<const bf16*>(x), ldx,
-                  batch_x, static_cast<const bf16*>(W), static_cast<bf16*>(out), batches, N, K);
+                  batch_x, static_cast<const bf16*>(W), static_cast<bf16*>(out), batches, N, K,
+                  static_cast<const float*>(freq), static_cast<const int*>(positions), rot_offset, rot, interleaved,
+                  static_cast<const bf16*>(gate), ldg);
   else if (out_dtype == PIH_F32)
     launch_kernel(batched_gemv_kernel<bf16, float>, grid, dim3(256), K * sizeof(float), s, static_cast<const bf16*>(x), ldx,
-                  batch_x, static_cast<const bf16*>(W), static_cast<float*>(out), batches, N, K);
+                  batch_x, static_cast<const bf16*>(W), static_cast<float*>(out), batches, N, K,
+                  static_cast<const float*>(freq), static_cast<const int*>(positions), rot_offset, rot, interleaved,
+                  static_cast<const bf16*>(gate), ldg);
   else
     return PIH_ERR_BAD_ARGUMENT;
   PIH_LAUNCH_CHECK();

@@ -256,12 +256,14 @@ class CudaOps:
     def linear_skinny(self, x: torch.Tensor, w: torch.Tensor, *, delta=None, norm_weight=None, eps: float = 0.0,
                       swiglu: bool = False, residual: Optional[torch.Tensor] = None, activation: str = "silu"):
         """The few-rows product (bf16, at most 16 rows) with its optional fused residual add, RMSNorm and
-        SwiGLU (``activation`` "gelu_tanh": GELU in SiLU's place) in front and behind.  ``residual``: the result is ``round(round(x . w^T) + residual)``.  Returns
+        SwiGLU (``activation`` "gelu_tanh": GELU in SiLU's place) in front and behind.  ``activation`` "relu2" without
+        ``swiglu``: the output is the square of ``max(round(x . w^T), 0)`` (a two-matrix feed-forward's first half).
+        ``residual``: the result is ``round(round(x . w^T) + residual)``.  Returns
         ``out`` — or ``(x + delta, out)`` when ``delta`` is given — or None when the kernel does not take the shape."""
         M, K = x.shape
         N = w.shape[0]
         if (x.dtype != torch.bfloat16 or M > 16 or K % 32 or K > 16384 or x.stride(1) != 1 or w.stride(1) != 1
-                or (swiglu and (N % 16 or residual is not None))
+                or (swiglu and (N % 16 or residual is not None)) or (not swiglu and activation == "relu2" and residual is not None)
                 or (residual is not None and (residual.shape != (M, N) or not residual.is_contiguous()))):
             return None
         out = torch.empty(M, N // 2 if swiglu else N, dtype=torch.bfloat16, device=x.device)
@@ -269,7 +271,8 @@ class CudaOps:
         nd = _DT[norm_weight.dtype] if norm_weight is not None else 0
         rc = self.lib.pih_gemm_skinny(_ptr(x), _ptr(delta), _ptr(x_out), nd, _ptr(norm_weight), c_float(eps), _ptr(w),
                                       _ptr(out), _ptr(residual), M, N, K, c_ll(x.stride(0)), c_ll(w.stride(0)),
-                                      c_ll(out.stride(0)), (2 if activation == "gelu_tanh" else 1) if swiglu else 0,
+                                      c_ll(out.stride(0)),
+                                      (2 if activation == "gelu_tanh" else 1) if swiglu else (3 if activation == "relu2" else 0),
                                       self._err(), self._stream())
         if rc == -2:
             return None
@@ -631,24 +634,45 @@ class CudaOps:
         self._check(rc, "rmsnorm_stream")
         return out
 
-    def linear_batched(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    def linear_batched(self, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+                       rotate: Optional[dict] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``out[t, b] = x[t, b] . w[b]^T``: x ``[T, B, K]`` (a view whose rows may be strided), w ``[B, N, K]``;
-        32-bit accumulation in ascending k; out ``[T, B, N]`` contiguous."""
+        32-bit accumulation in ascending k; out ``[T, B, N]`` contiguous.
+
+        ``rotate`` (the arguments of ``rotate_heads``: offset, frequencies, interleaved, positions): part of every
+        ``x[t, b]`` is rotated first; ``gate`` ``[T, B N]`` (a view): the output times its sigmoid, column by column.
+        Few rows in bf16 do both inside the product's kernel; otherwise ``rotate_heads`` runs before the product and
+        ``gate_mul`` behind it (the same values: each step rounds where the separate kernel would)."""
         T, B, K = x.shape
         N = w.shape[1]
         out_dtype = out_dtype or x.dtype
         assert w.shape == (B, N, K) and w.is_contiguous() and x.dtype == w.dtype and x.stride(2) == 1
+        fused = (x.dtype == torch.bfloat16 and T <= self.skinny_max_rows and K % 8 == 0 and K <= 12288
+                 and T * B <= 65535 * 16 and (gate is None or (out_dtype == torch.bfloat16 and gate.dtype == torch.bfloat16)))
+        if (rotate is not None or gate is not None) and not fused:
+            if rotate is not None:
+                x = self.rotate_heads(x, **rotate)
+            out = self.linear_batched(x, w, out_dtype)
+            if gate is not None:
+                out = self.gate_mul(out.view(T, B * N), gate, "sigmoid").view(T, B, N)
+            return out
         if x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16 and T >= self.batched_library_min_rows:
             # many rows in bf16: the library's batched product (32-bit accumulation), as the single products of many rows
             return torch.bmm(x.transpose(0, 1), w.transpose(1, 2)).transpose(0, 1).contiguous()
         out = torch.empty(T, B, N, dtype=out_dtype, device=x.device)
         if x.dtype == torch.bfloat16 and T <= self.skinny_max_rows and K % 8 == 0:
             # few rows in bf16: a warp an output column, the small matrices' rows streamed once
+            freq = rotate["frequencies"] if rotate is not None else None
             rc = self.lib.pih_batched_gemv(_DT[out_dtype], _ptr(x), c_ll(x.stride(0)), c_ll(x.stride(1)), _ptr(w), _ptr(out),
-                                           T, B, N, K, self._stream())
+                                           T, B, N, K, _ptr(freq), _ptr(rotate["positions"] if rotate is not None else None),
+                                           rotate["offset"] if rotate is not None else 0,
+                                           2 * freq.shape[0] if freq is not None else 0,
+                                           1 if (rotate is not None and rotate["interleaved"]) else 0, _ptr(gate),
+                                           c_ll(gate.stride(0) if gate is not None else 0), self._stream())
             if rc != -2:
                 self._check(rc, "batched_gemv")
                 return out
+            assert rotate is None and gate is None, "the few-rows batched product refused a shape it was asked to fuse"
         rc = self.lib.pih_gemm_simt_batched(_DT[x.dtype], _DT[out_dtype], _ptr(x), _ptr(w), _ptr(out), T, N, K,
                                             c_ll(x.stride(0)), c_ll(K), c_ll(B * N), B, c_ll(x.stride(1)), c_ll(N * K),
                                             c_ll(N), self._stream())

@@ -129,14 +129,12 @@ class LatentAttention:
             cq = ops.latent_write(proj[:, F:F + R + rot], self.down_norm, s.norm_eps, cache.kv, cache.slot_mapping,
                                   query_latent=proj[:, :F], query_weight=self.q_norm, **rotation)
             q = ops.linear(cq, self.w_q_up).view(T, H, D + rot)
-        if rot:
-            q = ops.rotate_heads(q, offset=D, **rotation)                   # the last ``rot`` columns of every head
-        q_lat = ops.linear_batched(q, self.w_fold_k)                                            # [T, H, C]
+        # the last ``rot`` columns of every head are rotated on the way into the fold (few rows: inside its kernel)
+        q_lat = ops.linear_batched(q, self.w_fold_k, rotate=dict(offset=D, **rotation) if rot else None)   # [T, H, C]
         gate = proj[:, F + R + rot:] if s.gated else None
         o_lat = ops.latent_attention(q_lat, gate=gate if self.gate_per == "head" else None, sink=self.sink,
                                      cache=cache.kv, block_table=cache.block_table, step=step, scale=s.scale,
                                      window=cache.window or 0)
-        heads_out = ops.linear_batched(o_lat, self.w_up_v).view(T, H * V)                       # [T, H V]
-        if gate is not None and self.gate_per == "column":
-            heads_out = ops.gate_mul(heads_out, gate, "sigmoid")
-        return ops.linear(heads_out, self.w_o)
+        # the values' fold, and behind it the gate a column (few rows: in the fold's epilogue)
+        heads_out = ops.linear_batched(o_lat, self.w_up_v, gate=gate if self.gate_per == "column" else None)
+        return ops.linear(heads_out.view(T, H * V), self.w_o)

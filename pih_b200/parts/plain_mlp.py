@@ -1,7 +1,8 @@
 """Two-matrix feed-forward without biases or gate: ``W_down act(W_up x)``.
 
 ``activation`` "relu2" is the square of ``max(z, 0)``.  The up product is rounded to the compute dtype; the
-activation is one kernel in 32-bit, rounded once; then the down product.
+activation is one kernel in 32-bit, rounded once; then the down product.  For few rows in bf16 the few-rows product
+applies the activation in its epilogue (on the product's rounding: the same values).
 """
 from __future__ import annotations
 
@@ -31,4 +32,9 @@ class PlainMLP:
 
     def forward(self, x):
         ops = self.rt.ops
-        return ops.linear(ops.activation(ops.linear(x, self.w_up), self.spec.activation), self.w_down)
+        act = None
+        if x.shape[0] <= getattr(ops, "skinny_max_rows", 0) and hasattr(ops, "linear_skinny"):
+            act = ops.linear_skinny(x, self.w_up, activation=self.spec.activation)      # None: not a shape it takes
+        if act is None:
+            act = ops.activation(ops.linear(x, self.w_up), self.spec.activation)
+        return ops.linear(act, self.w_down)

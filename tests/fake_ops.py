@@ -168,8 +168,14 @@ class FakeOps:
             v = h
         return (v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps) * weight).to(out_dtype)
 
-    def linear_batched(self, x, w, out_dtype=None):
-        return torch.einsum("tbk,bnk->tbn", x.float(), w.float()).to(out_dtype or x.dtype).contiguous()
+    def linear_batched(self, x, w, out_dtype=None, rotate=None, gate=None):
+        if rotate is not None:
+            x = self.rotate_heads(x, **rotate)
+        out = torch.einsum("tbk,bnk->tbn", x.float(), w.float()).to(out_dtype or x.dtype).contiguous()
+        if gate is not None:
+            T, B, N = out.shape
+            out = self.gate_mul(out.view(T, B * N), gate, "sigmoid").view(T, B, N)
+        return out
 
     @staticmethod
     def _requests(step):

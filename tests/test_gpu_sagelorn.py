@@ -252,7 +252,44 @@ def test_row_wise_kernels():
     assert ops.scale_(z, 0.3) is z and float((z - keep * 0.3).abs().max()) < 1e-7
     got = ops.add_gated(a.to(DEV), a.to(DEV) * 2, None).double().cpu()
     assert float((got - 3 * a.double()).abs().max()) < 1e-5
+    # the squared ReLU in the few-rows product's epilogue: the bits of the product followed by the activation's kernel
+    for m, n, k in ((5, 96, 64), (16, 520, 256), (8, 4096, 1024)):
+        xb = (torch.randn(m, k, generator=g) * 0.5).bfloat16().to(DEV)
+        wb = (torch.randn(n, k, generator=g) * 0.1).bfloat16().to(DEV)
+        fused = ops.linear_skinny(xb, wb, activation="relu2")
+        assert fused is not None and torch.equal(fused, ops.activation(ops.linear(xb, wb), "relu2"))
+        ref = torch.relu((xb.double() @ wb.double().T).bfloat16().double()) ** 2
+        assert float((fused.double() - ref).abs().max()) <= 0.02 * float(ref.abs().max())
     ops.check_errors()
+
+
+@pytest.mark.parametrize("neighbours", [True, False])
+def test_the_few_rows_fold_rotates_and_gates_like_the_separate_kernels(neighbours):
+    """A batched product of few rows with the rotation of part of every head on its way in and the sigmoid gate a column
+    on its way out gives the bits of ``rotate_heads``, the product and ``gate_mul`` one after the other (which is also
+    what many rows run); and the values of the plain computation."""
+    ops = _ops()
+    g = torch.Generator().manual_seed(8)
+    T, B, K, N, offset, rot = 7, 3, 40, 24, 16, 16
+    x = (torch.randn(T, 5 + B * K, generator=g) * 0.7).bfloat16().to(DEV)[:, 5:].view(T, B, K)     # rows strided
+    w = (torch.randn(B, N, K, generator=g) * 0.3).bfloat16().to(DEV)
+    gate = torch.randn(T, B * N + 3, generator=g).bfloat16().to(DEV)[:, :B * N]
+    rot_cfg = {"dims": rot, "base": 40.0}
+    positions = [0, 3, 900, 17, 2, 64, 65]
+    rotate = dict(offset=offset, frequencies=plain.frequencies(rot_cfg).float().to(DEV), interleaved=neighbours,
+                  positions=torch.tensor(positions, dtype=torch.int32, device=DEV))
+    fused = ops.linear_batched(x, w, rotate=rotate, gate=gate)
+    apart = ops.gate_mul(ops.linear_batched(ops.rotate_heads(x, **rotate), w).view(T, B * N), gate, "sigmoid").view(T, B, N)
+    ops.check_errors()
+    assert torch.equal(fused, apart)
+    many = ops.linear_batched(x.repeat(30, 1, 1), w, rotate=dict(rotate, positions=rotate["positions"].repeat(30)),
+                              gate=gate.repeat(30, 1))
+    assert float((many[:T].double() - fused.double()).abs().max()) <= 0.02 * float(fused.double().abs().max())
+    xd = x.double().cpu()
+    turned = torch.cat([xd[..., :offset], plain.rotate(xd[..., offset:offset + rot], torch.tensor(positions), rot_cfg, neighbours),
+                        xd[..., offset + rot:]], dim=-1)
+    ref = torch.einsum("tbk,bnk->tbn", turned, w.double().cpu()) * torch.sigmoid(gate.double().cpu()).view(T, B, N)
+    assert float((fused.double().cpu() - ref).abs().max()) < 0.03 * float(ref.abs().max())
 
 
 def test_queries_alone_are_normed_and_rotated_and_nothing_is_written():
